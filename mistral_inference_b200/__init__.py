@@ -9,3 +9,5 @@ from .args import MoeArgs, TransformerArgs  # noqa: F401
 from .cache import BufferCache  # noqa: F401
 from .generate import generate  # noqa: F401  (the function; the submodule stays importable as mistral_inference_b200.generate)
 from .transformer import Transformer  # noqa: F401
+from .layered import LayeredTransformer  # noqa: F401
+from .registry import load_model  # noqa: F401

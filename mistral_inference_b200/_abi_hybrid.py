@@ -1,0 +1,130 @@
+"""ctypes binding of libmb200_hybrid.so (C ABI: include/mistral_b200_hybrid.h): the kernels of layered decoders.
+
+Same rules as `_abi`: the only place Python touches this library, and no fallback -- a missing library is built once
+in-tree by `build.build_hybrid()` (a fresh checkout has no binaries), a failing call raises.
+"""
+import ctypes
+from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
+from typing import Optional
+
+import torch
+
+from . import build
+from ._abi import Mb200Error
+
+ABI_VERSION = 1
+EPI_STORE, EPI_RESIDUAL, EPI_GLU, EPI_F32 = 0, 1, 2, 3
+_DT = {torch.bfloat16: 0, torch.float32: 1}
+_lib: Optional[ctypes.CDLL] = None
+
+P, I, F = c_void_p, c_int64, c_float
+_SIGNATURES = {
+    "mbh_abi_version": (c_int, []),
+    "mbh_last_error": (c_char_p, []),
+    "mbh_embed_scale": (c_int, [P, P, F, P, I, I, c_int, P]),
+    "mbh_rmsnorm": (c_int, [P, P, P, I, I, F, c_int, P]),
+    "mbh_linear": (c_int, [P, P, P, P, P, I, I, I, c_int, I, F, F, c_int, P]),
+    "mbh_attn_prep": (c_int, [P, P, P, P, P, P, P, P, P, P, c_int, I, I, I, I, I, F, F, I, c_int, P]),
+    "mbh_attn_bias": (c_int, [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, c_int, P]),
+    "mbh_lightning_scan": (c_int, [P, P, P, P, P, P, P, I, I, I, I, c_int, P]),
+    "mbh_gated_headnorm": (c_int, [P, P, P, I, I, P, I, I, F, c_int, P]),
+}
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        path = build.build_hybrid()
+        handle = ctypes.CDLL(str(path))
+        for name, (restype, argtypes) in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype, fn.argtypes = restype, argtypes
+        if handle.mbh_abi_version() != ABI_VERSION:
+            raise Mb200Error(f"libmb200_hybrid ABI {handle.mbh_abi_version()} != expected {ABI_VERSION}")
+        _lib = handle
+    return _lib
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = lib().mbh_last_error()
+        raise Mb200Error(f"{what} failed ({rc}): {msg.decode() if msg else '?'}")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    assert t.is_cuda and t.is_contiguous(), "libmb200_hybrid takes contiguous CUDA tensors"
+    return t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def dt_of(dtype: torch.dtype) -> int:
+    if dtype not in _DT:
+        raise Mb200Error(f"layered decoders store activations and weights as bfloat16 or float32, not {dtype}")
+    return _DT[dtype]
+
+
+def embed_scale(tokens: torch.Tensor, table: torch.Tensor, scale: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    T, D = tokens.shape[0], table.shape[1]
+    assert tokens.dtype == torch.long
+    out = torch.empty(T, D, dtype=torch.float32, device=table.device) if out is None else out
+    _check(lib().mbh_embed_scale(_ptr(tokens), _ptr(table), scale, _ptr(out), T, D, dt_of(table.dtype), _stream()), "mbh_embed_scale")
+    return out
+
+
+def rmsnorm(x32: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    T, D = x32.shape
+    assert x32.dtype == torch.float32
+    y = torch.empty(T, D, dtype=w.dtype, device=x32.device)
+    _check(lib().mbh_rmsnorm(_ptr(x32), _ptr(w), _ptr(y), T, D, eps, dt_of(w.dtype), _stream()), "mbh_rmsnorm")
+    return y
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, *, epi: int = EPI_STORE, n_act: int = 0,
+           residual: Optional[torch.Tensor] = None, limit: float = 0.0, alpha: float = 0.0) -> torch.Tensor:
+    """x [M, K] @ w [N, K]^T with the epilogues of include/mistral_b200_hybrid.h.  EPI_RESIDUAL adds into `residual` (fp32, in
+    place) and returns it; EPI_F32 returns fp32 [M, N]; EPI_GLU returns [M, N/2]."""
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and x.dtype == w.dtype
+    out = out32 = None
+    if epi == EPI_RESIDUAL:
+        assert residual is not None and residual.dtype == torch.float32 and residual.shape == (M, N)
+        out32 = residual
+    elif epi == EPI_F32:
+        out32 = torch.empty(M, N, dtype=torch.float32, device=x.device)
+    else:
+        out = torch.empty(M, N // 2 if epi == EPI_GLU else N, dtype=x.dtype, device=x.device)
+    _check(lib().mbh_linear(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _ptr(out32), M, N, K, epi, n_act, limit, alpha, dt_of(x.dtype), _stream()),
+           "mbh_linear")
+    return out if out is not None else out32
+
+
+def attn_prep(qkv, qnorm, knorm, positions, cache_rows, q_out, cache_k, cache_v, v_first, vmix, vmix_mode: int, H: int, G: int, d: int, e: int,
+              eps: float, temp_coef: float, temp_every: int) -> None:
+    _check(lib().mbh_attn_prep(_ptr(qkv), _ptr(qnorm), _ptr(knorm), _ptr(positions), _ptr(cache_rows), _ptr(q_out), _ptr(cache_k), _ptr(cache_v),
+                               _ptr(v_first), _ptr(vmix), vmix_mode, qkv.shape[0], H, G, d, e, eps, temp_coef, temp_every, dt_of(qkv.dtype),
+                               _stream()), "mbh_attn_prep")
+
+
+def attn_bias(q, cache_k, cache_v, bias_tab, positions, q_start, slots, out, B: int, W: int, H: int, G: int, d: int, e: int, scale: float) -> None:
+    assert bias_tab.dtype == torch.float32 and bias_tab.shape[1] == H
+    _check(lib().mbh_attn_bias(_ptr(q), _ptr(cache_k), _ptr(cache_v), _ptr(bias_tab), bias_tab.shape[0], _ptr(positions), _ptr(q_start), _ptr(slots),
+                               _ptr(out), q.shape[0], B, W, H, G, d, e, scale, dt_of(q.dtype), _stream()), "mbh_attn_bias")
+
+
+def lightning_scan(qkvg, state, decay, q_start, seqpos, slots, o32, B: int, H: int, d: int, e: int) -> None:
+    assert state.dtype == torch.float32 and decay.dtype == torch.float32 and o32.dtype == torch.float32
+    _check(lib().mbh_lightning_scan(_ptr(qkvg), _ptr(state), _ptr(decay), _ptr(q_start), _ptr(seqpos), _ptr(slots), _ptr(o32), B, H, d, e,
+                                    dt_of(qkvg.dtype), _stream()), "mbh_lightning_scan")
+
+
+def gated_headnorm(o32, w, g, g_pitch: int, g_off: int, eps: float) -> torch.Tensor:
+    T, N = o32.shape
+    y = torch.empty(T, N, dtype=w.dtype, device=o32.device)
+    _check(lib().mbh_gated_headnorm(_ptr(o32), _ptr(w), _ptr(g), g_pitch, g_off, _ptr(y), T, N, eps, dt_of(w.dtype), _stream()), "mbh_gated_headnorm")
+    return y

@@ -64,5 +64,36 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     return LIB
 
 
+HYBRID_SRC = CSRC / "hybrid"
+HYBRID_LIB = PKG / "libmb200_hybrid.so"
+
+
+def build_hybrid(force: bool = False) -> Path:
+    """libmb200_hybrid.so: the kernels of layered decoders (csrc/hybrid/), a separate, small library so that a fresh checkout
+    that only serves such a model compiles only them (seconds).  Safe when several processes start at once: the output is
+    written under a private name and renamed."""
+    files = sorted(HYBRID_SRC.glob("*.cu")) + sorted(HYBRID_SRC.glob("*.cuh")) + [PKG.parent / "include" / "mistral_b200_hybrid.h"]
+    h = hashlib.sha256()
+    for f in files:
+        h.update(f.name.encode())
+        h.update(f.read_bytes())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    digest = h.hexdigest()
+    stamp = HYBRID_SRC / ".build_stamp"
+    if not force and HYBRID_LIB.exists() and stamp.exists() and stamp.read_text().strip() == digest:
+        return HYBRID_LIB
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    tmp = PKG / f".libmb200_hybrid.{os.getpid()}.so"
+    cmd = [nvcc, *NVCC_FLAGS, "-o", str(tmp)] + [str(f) for f in sorted(HYBRID_SRC.glob("*.cu"))]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        sys.stderr.write(proc.stdout + proc.stderr)
+        raise RuntimeError(f"nvcc failed ({proc.returncode}): {' '.join(cmd)}")
+    os.replace(tmp, HYBRID_LIB)
+    stamp.write_text(digest)
+    return HYBRID_LIB
+
+
 if __name__ == "__main__":
+    print(build_hybrid(force="--force" in sys.argv))
     print(build_library(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

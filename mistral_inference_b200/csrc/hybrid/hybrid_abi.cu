@@ -1,0 +1,133 @@
+// C ABI of libmb200_hybrid.so: the kernels of layered decoders (per-layer mixer kinds, fp32 residual stream, bf16 or fp32
+// storage).  Declarations: include/mistral_b200_hybrid.h.  `dt` selects the storage type of activations and weights:
+// 0 = bf16, 1 = fp32.  Every call returns 0 or a CUDA error code; mbh_last_error() gives the text.
+#include "hybrid_linear.cuh"
+#include "hybrid_mixers.cuh"
+#include "../../../include/mistral_b200_hybrid.h"
+
+#include <stdio.h>
+
+using namespace mbh;
+
+static thread_local char g_err[256] = "";
+
+static int fail(cudaError_t e, const char* what) {
+    snprintf(g_err, sizeof(g_err), "%s: %s", what, cudaGetErrorString(e));
+    return (int)e;
+}
+static int bad(const char* what) {
+    snprintf(g_err, sizeof(g_err), "%s", what);
+    return -1;
+}
+#define DISPATCH(dt, ...)                                   \
+    do {                                                    \
+        if ((dt) == 0) { using ST = bf16; __VA_ARGS__; }     \
+        else if ((dt) == 1) { using ST = float; __VA_ARGS__; } \
+        else return bad("dt must be 0 (bf16) or 1 (fp32)"); \
+    } while (0)
+
+template <typename T>
+static cudaError_t launch_lightning(const LightningArgs& a, cudaStream_t st) {
+    const int threads = a.e >= 128 ? 128 : ((a.e + 31) / 32) * 32;
+    dim3 grid(a.B * a.H, (a.e + threads - 1) / threads);
+    if (a.d <= 32) lightning_scan_kernel<T, 32><<<grid, threads, 0, st>>>(a);
+    else if (a.d <= 64) lightning_scan_kernel<T, 64><<<grid, threads, 0, st>>>(a);
+    else lightning_scan_kernel<T, 128><<<grid, threads, 0, st>>>(a);
+    return cudaGetLastError();
+}
+
+
+template <typename T> static void run_embed(const void* tokens, const void* table, float scale, void* x32, int64_t T_, int64_t D, cudaStream_t st) {
+    embed_scale_kernel<T><<<(unsigned)T_, 128, 0, st>>>((const int64_t*)tokens, (const T*)table, scale, (float*)x32, (int)D);
+}
+template <typename T> static void run_rmsnorm(const void* x32, const void* w, void* y, int64_t T_, int64_t D, float eps, cudaStream_t st) {
+    rmsnorm_f32_kernel<T><<<(unsigned)T_, D >= 1024 ? 256 : 128, 0, st>>>((const float*)x32, (const T*)w, (T*)y, (int)D, eps);
+}
+template <typename T> static void run_prep(const AttnPrepArgs& a, int64_t T_, cudaStream_t st) { attn_prep_kernel<T><<<(unsigned)T_, 128, 0, st>>>(a); }
+template <typename T> static void run_attn(const AttnArgs& a, size_t smem, cudaStream_t st) {
+    attn_bias_kernel<T><<<(unsigned)(a.T * a.H), AT_WARPS * 32, smem, st>>>(a);
+}
+template <typename T> static void run_headnorm(const void* o32, const void* w, const void* g, int64_t g_pitch, int64_t g_off, void* y, int64_t T_,
+                                               int64_t N, float eps, cudaStream_t st) {
+    gated_headnorm_kernel<T><<<(unsigned)T_, 128, 0, st>>>((const float*)o32, (const T*)w, (const T*)g, (int)g_pitch, (int)g_off, (T*)y, (int)N, eps);
+}
+
+extern "C" {
+
+int mbh_abi_version(void) { return MBH_ABI_VERSION; }
+const char* mbh_last_error(void) { return g_err; }
+
+int mbh_embed_scale(const void* tokens, const void* table, float scale, void* x32, int64_t T, int64_t D, int dt, void* stream) {
+    if (T == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, run_embed<ST>(tokens, table, scale, x32, T, D, st));
+    cudaError_t e = cudaGetLastError();
+    return e ? fail(e, "mbh_embed_scale") : 0;
+}
+
+int mbh_rmsnorm(const void* x32, const void* w, void* y, int64_t T, int64_t D, float eps, int dt, void* stream) {
+    if (T == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, run_rmsnorm<ST>(x32, w, y, T, D, eps, st));
+    cudaError_t e = cudaGetLastError();
+    return e ? fail(e, "mbh_rmsnorm") : 0;
+}
+
+int mbh_linear(const void* x, const void* w, const void* bias, void* out, void* out32, int64_t M, int64_t N, int64_t K, int epi, int64_t n_act,
+               float limit, float alpha, int dt, void* stream) {
+    if (epi < 0 || epi > 3) return bad("mbh_linear: unknown epilogue");
+    if (epi == EPI_GLU && (N & 1)) return bad("mbh_linear: the gated epilogue needs interleaved (even) rows");
+    LinearArgs a{x, w, bias, out, (float*)out32, (int)M, (int)N, (int)K, epi, (int)n_act, limit, alpha};
+    cudaError_t e = cudaSuccess;
+    DISPATCH(dt, e = launch_linear<ST>(a, (cudaStream_t)stream));
+    return e ? fail(e, "mbh_linear") : 0;
+}
+
+int mbh_attn_prep(const void* qkv, const void* qnorm, const void* knorm, const void* positions, const void* cache_rows, void* q_out, void* cache_k,
+                  void* cache_v, void* v_first, const void* vmix, int vmix_mode, int64_t T, int64_t H, int64_t G, int64_t d, int64_t e, float eps,
+                  float temp_coef, int64_t temp_every, int dt, void* stream) {
+    if (T == 0) return 0;
+    AttnPrepArgs a{qkv, qnorm, knorm, (const int*)positions, (const int*)cache_rows, q_out, cache_k, cache_v, v_first, vmix, vmix_mode,
+                   (int)H, (int)G, (int)d, (int)e, eps, temp_coef, (int)temp_every};
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, run_prep<ST>(a, T, st));
+    cudaError_t err = cudaGetLastError();
+    return err ? fail(err, "mbh_attn_prep") : 0;
+}
+
+int mbh_attn_bias(const void* q, const void* cache_k, const void* cache_v, const void* bias_tab, int64_t n_tab, const void* positions,
+                  const void* q_start, const void* slots, void* out, int64_t T, int64_t B, int64_t W, int64_t H, int64_t G, int64_t d, int64_t e,
+                  float scale, int dt, void* stream) {
+    if (T == 0) return 0;
+    if (e > 32 * AT_MAXR) return bad("mbh_attn_bias: value size above 256");
+    if (H % G) return bad("mbh_attn_bias: heads must be a multiple of kv heads");
+    AttnArgs a{q, cache_k, cache_v, (const float*)bias_tab, (int)n_tab, (const int*)positions, (const int*)q_start, (const int*)slots, out,
+               (int)T, (int)B, (int)W, (int)H, (int)G, (int)d, (int)e, scale};
+    const size_t smem = sizeof(float) * ((size_t)d + AT_WARPS * AT_CHUNK + AT_WARPS * (2 + 32 * AT_MAXR));
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, run_attn<ST>(a, smem, st));
+    cudaError_t err = cudaGetLastError();
+    return err ? fail(err, "mbh_attn_bias") : 0;
+}
+
+int mbh_lightning_scan(const void* qkvg, void* state, const void* decay, const void* q_start, const void* seqpos, const void* slots, void* o32,
+                       int64_t B, int64_t H, int64_t d, int64_t e, int dt, void* stream) {
+    if (B == 0) return 0;
+    if (d > 128) return bad("mbh_lightning_scan: key size above 128");
+    LightningArgs a{qkvg, (float*)state, (const float*)decay, (const int*)q_start, (const int*)seqpos, (const int*)slots, (float*)o32,
+                    (int)B, (int)H, (int)d, (int)e};
+    cudaError_t err = cudaSuccess;
+    DISPATCH(dt, err = launch_lightning<ST>(a, (cudaStream_t)stream));
+    return err ? fail(err, "mbh_lightning_scan") : 0;
+}
+
+int mbh_gated_headnorm(const void* o32, const void* w, const void* g, int64_t g_pitch, int64_t g_off, void* y, int64_t T, int64_t N, float eps,
+                       int dt, void* stream) {
+    if (T == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, run_headnorm<ST>(o32, w, g, g_pitch, g_off, y, T, N, eps, st));
+    cudaError_t err = cudaGetLastError();
+    return err ? fail(err, "mbh_gated_headnorm") : 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,277 @@
+// Token mixers of the layered decoder and the elementwise steps around them.
+//
+//   embed_scale       x[t] = E[token[t]] * scale                       -> fp32 residual stream
+//   rmsnorm_f32       y = x / sqrt(mean(x^2) + eps) * w                 fp32 in, storage type out
+//   attn_prep         per-head RMS norm of q and k (shared weight), query temperature by position, value mixing with an
+//                     earlier layer's values, scatter of k and v into the layer's cache ring
+//   attn_bias         causal softmax attention over the ring with a per-(distance, head) additive bias, GQA, separate
+//                     key and value sizes; one kernel for prompts, prompt portions and decode
+//   lightning_scan    decayed linear attention S <- a S + k v^T, o = S^T q with the fp32 state carried in the cache
+//   gated_headnorm    y = rms(o over all heads) * w * sigmoid(g)
+#pragma once
+#include "hybrid_common.cuh"
+
+namespace mbh {
+
+// ------------------------------------------------------------------------------------------------ embedding, norm
+template <typename T>
+__global__ void embed_scale_kernel(const int64_t* __restrict__ tok, const T* __restrict__ E, float scale, float* __restrict__ x, int D) {
+    const T* row = E + (size_t)tok[blockIdx.x] * D;
+    float* o = x + (size_t)blockIdx.x * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = to_f(row[i]) * scale;
+}
+
+template <typename T>
+__global__ void rmsnorm_f32_kernel(const float* __restrict__ x, const T* __restrict__ w, T* __restrict__ y, int D, float eps) {
+    __shared__ float red[32];
+    const float* r = x + (size_t)blockIdx.x * D;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) ss = fmaf(r[i], r[i], ss);
+    ss = block_sum(ss, red);
+    const float inv = 1.f / sqrtf(ss / (float)D + eps);
+    T* o = y + (size_t)blockIdx.x * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = from_f<T>(r[i] * inv * to_f(w[i]));
+}
+
+// ------------------------------------------------------------------------------------------------ attention: q/k/v preparation
+struct AttnPrepArgs {
+    const void* qkv;       // [T, H*d + G*d + G*e] projections with bias
+    const void* qnorm; const void* knorm;   // [d] each, or null (no norm)
+    const int* positions;  // [T]
+    const int* cache_rows; // [T] flat ring row (slot * W + pos % W) or -1
+    void* q_out;           // [T, H*d]
+    void* cache_k; void* cache_v;  // [rows, G, d] / [rows, G, e]
+    void* v_first;         // [T, G*e]: written when vmix_mode == 1, read when == 2
+    const void* vmix;      // scalar lambda (storage type), vmix_mode == 2
+    int vmix_mode;
+    int H, G, d, e;
+    float eps, temp_coef; int temp_every;  // temperature 1 + coef * ln(floor((p + 1) / every) + 1); every == 0: none
+};
+
+template <typename T>
+__global__ void attn_prep_kernel(AttnPrepArgs a) {
+    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const int Nq = a.H * a.d, Nk = a.G * a.d, Nv = a.G * a.e;
+    const T* row = static_cast<const T*>(a.qkv) + (size_t)t * (Nq + Nk + Nv);
+    const int pos = a.positions[t];
+    const int crow = a.cache_rows ? a.cache_rows[t] : -1;
+    float temp = 1.f;
+    if (a.temp_every > 0) temp = 1.f + a.temp_coef * logf((float)((pos + 1) / a.temp_every + 1));
+    for (int h = warp; h < a.H + a.G; h += nw) {
+        const bool is_q = h < a.H;
+        const T* src = row + (is_q ? h * a.d : Nq + (h - a.H) * a.d);
+        const T* nwgt = static_cast<const T*>(is_q ? a.qnorm : a.knorm);
+        float ss = 0.f;
+        for (int i = lane; i < a.d; i += 32) { float v = to_f(src[i]); ss = fmaf(v, v, ss); }
+        ss = warp_sum(ss);
+        const float inv = nwgt ? 1.f / sqrtf(ss / (float)a.d + a.eps) : 1.f;
+        T* dst;
+        if (is_q) dst = static_cast<T*>(a.q_out) + (size_t)t * Nq + h * a.d;
+        else { if (crow < 0) continue; dst = static_cast<T*>(a.cache_k) + (size_t)crow * Nk + (h - a.H) * a.d; }
+        for (int i = lane; i < a.d; i += 32) {
+            float v = to_f(src[i]) * inv * (nwgt ? to_f(nwgt[i]) : 1.f);
+            if (is_q) v = rnd<T>(v) * temp;
+            dst[i] = from_f<T>(v);
+        }
+    }
+    const T* vsrc = row + Nq + Nk;
+    T* vf = static_cast<T*>(a.v_first) + (size_t)t * Nv;
+    const float lam = a.vmix_mode == 2 ? to_f(*static_cast<const T*>(a.vmix)) : 0.f;
+    for (int i = threadIdx.x; i < Nv; i += blockDim.x) {
+        float v = to_f(vsrc[i]);
+        if (a.vmix_mode == 1) vf[i] = vsrc[i];
+        else if (a.vmix_mode == 2) v = (1.f - lam) * v + lam * to_f(vf[i]);
+        if (crow >= 0) static_cast<T*>(a.cache_v)[(size_t)crow * Nv + i] = from_f<T>(v);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ attention core
+struct AttnArgs {
+    const void* q;          // [T, H*d]
+    const void* cache_k; const void* cache_v;
+    const float* bias_tab;  // [n_tab, H] additive bias by distance; distances >= n_tab use row n_tab - 1
+    int n_tab;
+    const int* positions;   // [T]
+    const int* q_start;     // [B + 1]
+    const int* slots;       // [B] physical cache row block of each sequence
+    void* out;              // [T, H*e]
+    int T, B, W, H, G, d, e;
+    float scale;
+};
+
+constexpr int AT_WARPS = 4, AT_CHUNK = 128, AT_MAXR = 8;  // e <= 32 * AT_MAXR
+
+// One CTA per (token, head); its warps take alternate chunks of AT_CHUNK keys (scores: lanes over keys; values: lanes
+// over the value columns) with a running (max, sum); the warps' partial results are merged through shared memory.
+template <typename T>
+__global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(AttnArgs a) {
+    extern __shared__ float sm[];
+    const int t = blockIdx.x / a.H, h = blockIdx.x % a.H, g = h / (a.H / a.G);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* qs = sm;                                  // [d]
+    float* sc = sm + a.d + warp * AT_CHUNK;          // [AT_CHUNK] per warp
+    float* mrg = sm + a.d + AT_WARPS * AT_CHUNK;     // [AT_WARPS][2 + 32 * AT_MAXR]
+    int b = 0;
+    while (b + 1 < a.B && a.q_start[b + 1] <= t) ++b;
+    const int pos = a.positions[t], n = pos + 1;
+    const T* q = static_cast<const T*>(a.q) + ((size_t)t * a.H + h) * a.d;
+    for (int i = threadIdx.x; i < a.d; i += blockDim.x) qs[i] = to_f(q[i]) * a.scale;
+    __syncthreads();
+    const size_t base = (size_t)a.slots[b] * a.W;
+    const T* K = static_cast<const T*>(a.cache_k) + base * a.G * a.d + (size_t)g * a.d;
+    const T* Vp = static_cast<const T*>(a.cache_v) + base * a.G * a.e + (size_t)g * a.e;
+    const size_t ks = (size_t)a.G * a.d, vs = (size_t)a.G * a.e;
+    constexpr int V = Vec<T>::N;
+    const bool vec_ok = (a.d % V == 0) && (reinterpret_cast<uintptr_t>(a.cache_k) % 16 == 0);
+    float m = -INFINITY, l = 0.f, acc[AT_MAXR];
+#pragma unroll
+    for (int r = 0; r < AT_MAXR; ++r) acc[r] = 0.f;
+    for (int c0 = warp * AT_CHUNK; c0 < n; c0 += AT_WARPS * AT_CHUNK) {
+        const int cn = min(AT_CHUNK, n - c0);
+        float cmax = -INFINITY;
+        for (int jj = lane; jj < cn; jj += 32) {
+            const int j = c0 + jj;
+            const T* kr = K + (size_t)(j % a.W) * ks;
+            float s = 0.f;
+            if (vec_ok) {
+                for (int i = 0; i < a.d; i += V) {
+                    float kv[V];
+                    Vec<T>::load(kr + i, kv);
+#pragma unroll
+                    for (int u = 0; u < V; ++u) s = fmaf(qs[i + u], kv[u], s);
+                }
+            } else {
+                for (int i = 0; i < a.d; ++i) s = fmaf(qs[i], to_f(kr[i]), s);
+            }
+            const int dist = min(pos - j, a.n_tab - 1);
+            s += a.bias_tab[(size_t)dist * a.H + h];
+            sc[jj] = s;
+            cmax = fmaxf(cmax, s);
+        }
+        cmax = warp_max(cmax);
+        const float m_new = fmaxf(m, cmax);
+        const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
+        float psum = 0.f;
+        for (int jj = lane; jj < cn; jj += 32) { float p = expf(sc[jj] - m_new); sc[jj] = p; psum += p; }
+        psum = warp_sum(psum);
+        l = l * corr + psum;
+        m = m_new;
+        __syncwarp();
+#pragma unroll
+        for (int r = 0; r < AT_MAXR; ++r) {
+            const int col = lane + 32 * r;
+            if (col < a.e) {
+                float o = acc[r] * corr;
+                const T* vp = Vp + col;
+                for (int jj = 0; jj < cn; ++jj) o = fmaf(sc[jj], to_f(vp[(size_t)((c0 + jj) % a.W) * vs]), o);
+                acc[r] = o;
+            }
+        }
+        __syncwarp();
+    }
+    // merge the warps
+    float* mine = mrg + warp * (2 + 32 * AT_MAXR);
+    if (lane == 0) { mine[0] = m; mine[1] = l; }
+#pragma unroll
+    for (int r = 0; r < AT_MAXR; ++r) mine[2 + r * 32 + lane] = acc[r];
+    __syncthreads();
+    if (warp == 0) {
+        float M = -INFINITY;
+        for (int w = 0; w < AT_WARPS; ++w) M = fmaxf(M, mrg[w * (2 + 32 * AT_MAXR)]);
+        float L = 0.f, o[AT_MAXR];
+#pragma unroll
+        for (int r = 0; r < AT_MAXR; ++r) o[r] = 0.f;
+        for (int w = 0; w < AT_WARPS; ++w) {
+            const float* p = mrg + w * (2 + 32 * AT_MAXR);
+            if (p[0] == -INFINITY) continue;
+            const float f = expf(p[0] - M);
+            L += p[1] * f;
+#pragma unroll
+            for (int r = 0; r < AT_MAXR; ++r) o[r] = fmaf(p[2 + r * 32 + lane], f, o[r]);
+        }
+        T* out = static_cast<T*>(a.out) + ((size_t)t * a.H + h) * a.e;
+#pragma unroll
+        for (int r = 0; r < AT_MAXR; ++r) {
+            const int col = lane + 32 * r;
+            if (col < a.e) out[col] = from_f<T>(o[r] / L);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ lightning attention
+struct LightningArgs {
+    const void* qkvg;      // [T, 2*H*d + 2*H*e]: q | k | v (activated) | g
+    float* state;          // [slots, H, d, e] fp32
+    const float* decay;    // [H]
+    const int* q_start;    // [B + 1]
+    const int* seqpos;     // [B] tokens before this call (0: the state starts at zero)
+    const int* slots;      // [B]
+    float* o;              // [T, H*e] fp32
+    int B, H, d, e;
+};
+
+constexpr int LS_TB = 16;
+
+// One CTA per (sequence, head, block of value columns); thread c owns column c of the state: DMAX registers.  Keys and queries
+// of LS_TB tokens at a time are staged through shared memory.  Sequential in t, exact in fp32.
+template <typename T, int DMAX>
+__global__ void lightning_scan_kernel(LightningArgs a) {
+    __shared__ float ks[LS_TB][DMAX], qs[LS_TB][DMAX];
+    const int b = blockIdx.x / a.H, h = blockIdx.x % a.H;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    const bool live = c < a.e;
+    const int t0 = a.q_start[b], t1 = a.q_start[b + 1];
+    const int stride = 2 * a.H * a.d + 2 * a.H * a.e;
+    const T* X = static_cast<const T*>(a.qkvg);
+    float* st = a.state + (((size_t)a.slots[b] * a.H + h) * a.d) * a.e;
+    const float dec = a.decay[h];
+    float S[DMAX];
+    const bool fresh = a.seqpos[b] == 0;
+#pragma unroll
+    for (int i = 0; i < DMAX; ++i) S[i] = (live && !fresh && i < a.d) ? st[(size_t)i * a.e + c] : 0.f;
+    for (int tb = t0; tb < t1; tb += LS_TB) {
+        const int nt = min(LS_TB, t1 - tb);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < nt * DMAX; idx += blockDim.x) {
+            const int tt = idx / DMAX, i = idx % DMAX;
+            const T* row = X + (size_t)(tb + tt) * stride;
+            qs[tt][i] = i < a.d ? to_f(row[h * a.d + i]) : 0.f;
+            ks[tt][i] = i < a.d ? to_f(row[a.H * a.d + h * a.d + i]) : 0.f;
+        }
+        __syncthreads();
+        if (live) {
+            for (int tt = 0; tt < nt; ++tt) {
+                const float v = to_f(X[(size_t)(tb + tt) * stride + 2 * a.H * a.d + h * a.e + c]);
+                float o = 0.f;
+#pragma unroll
+                for (int i = 0; i < DMAX; ++i) {
+                    S[i] = fmaf(dec, S[i], ks[tt][i] * v);
+                    o = fmaf(S[i], qs[tt][i], o);
+                }
+                a.o[(size_t)(tb + tt) * a.H * a.e + h * a.e + c] = o;
+            }
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < DMAX; ++i)
+            if (i < a.d) st[(size_t)i * a.e + c] = S[i];
+    }
+}
+
+// y[t, :] = o[t, :] / sqrt(mean(o[t]^2) + eps) * w * sigmoid(g[t, :]); g lives at column `g_off` of rows of pitch `g_pitch`
+template <typename T>
+__global__ void gated_headnorm_kernel(const float* __restrict__ o, const T* __restrict__ w, const T* __restrict__ g, int g_pitch, int g_off,
+                                      T* __restrict__ y, int N, float eps) {
+    __shared__ float red[32];
+    const float* r = o + (size_t)blockIdx.x * N;
+    const T* gr = g + (size_t)blockIdx.x * g_pitch + g_off;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < N; i += blockDim.x) ss = fmaf(r[i], r[i], ss);
+    ss = block_sum(ss, red);
+    const float inv = 1.f / sqrtf(ss / (float)N + eps);
+    for (int i = threadIdx.x; i < N; i += blockDim.x)
+        y[(size_t)blockIdx.x * N + i] = from_f<T>(r[i] * inv * to_f(w[i]) * sigmoid_exact(to_f(gr[i])));
+}
+
+}  // namespace mbh

@@ -63,10 +63,7 @@ def generate(encoded_prompts: List[List[int]], model: Transformer, images: List[
     B, V = plan.B, model.args.vocab_size
 
     # one ring per layer, sized like the reference's (generate.py:68-78)
-    cache = BufferCache(model.n_local_layers, model.args.max_batch_size, max(plan.lens) + max_tokens, model.args.n_kv_heads,
-                        model.args.head_dim, model.args.sliding_window)
-    cache.to(device=dev, dtype=model.dtype)
-    cache.reset()
+    cache = model.make_cache(model.args.max_batch_size, max(plan.lens) + max_tokens)
 
     # ---- prompt: hidden states chunk by chunk, log-probabilities fused with the lm head ----
     prompt_lp: List[torch.Tensor] = []

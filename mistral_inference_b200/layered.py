@@ -1,0 +1,225 @@
+"""Layered decoder: a model given as a list of layers, each with its own kind of token mixer (softmax attention with a
+distance bias, lightning attention with a recurrent state, ...) and an optional feed-forward (args.LayeredArgs; architecture
+"Fesenex").  It plugs into the same places as `Transformer`: `from_folder`, `forward(input_ids, seqlens, cache)` over ragged
+batches, `BufferCache` (per-layer rings and states, `make_cache`), `forward_logprobs` / `next_token_logits` for `generate()`.
+
+On disk: config.json + model.safetensors with tensors `embed`, `l<i>.norm1|norm2`, `l<i>.mix.*`, `l<i>.mlp.gate|up|down`,
+`final.norm`, `head`.  The residual stream is fp32; weights and activations are bf16 or fp32 (`dtype`), the latter in true
+fp32 arithmetic.  All compute runs in libmb200_hybrid.so (include/mistral_b200_hybrid.h); CUDA only, no fallback.
+"""
+import json
+from pathlib import Path
+from typing import Any, Dict, List, Optional, Tuple, Union
+
+import torch
+from torch import nn
+
+from . import _abi, _abi_hybrid as _h
+from .args import LayeredArgs
+from .cache import BufferCache
+from .transformer_layers import MIXERS, BiasedAttention, ClampedGLU, LayeredBlock, LightningMixer
+
+
+class LayeredTransformer(nn.Module):
+    def __init__(self, args: LayeredArgs, softmax_fp32: bool = True):
+        super().__init__()
+        self.args = args
+        self.vocab_size = args.vocab
+        self.n_layers = self.n_local_layers = len(args.layers)
+        self.embed = nn.Parameter(torch.empty(args.vocab, args.width), requires_grad=False)
+        blocks = []
+        seen_vmix = False
+        for L in args.layers:
+            if L.type == "attention":
+                mixer: nn.Module = BiasedAttention(args.width, L.mixer, args.norm_eps, first_vmix=L.mixer.v_mix and not seen_vmix)
+                seen_vmix = seen_vmix or L.mixer.v_mix
+            else:
+                mixer = MIXERS[L.type](args.width, L.mixer, args.norm_eps)
+            blocks.append(LayeredBlock(args.width, args.norm_eps, mixer, ClampedGLU(args.width, L.mlp) if L.mlp is not None else None))
+        self.layers = nn.ModuleList(blocks)
+        self.final_norm = nn.Parameter(torch.empty(args.width), requires_grad=False)
+        self.head = nn.Parameter(torch.empty(args.vocab, args.width), requires_grad=False)
+        self.last_argmax: Optional[torch.Tensor] = None
+
+    # ------------------------------------------------------------------ properties
+    @property
+    def dtype(self) -> torch.dtype:
+        return self.embed.dtype
+
+    @property
+    def device(self) -> torch.device:
+        return self.embed.device
+
+    def make_cache(self, max_batch_size: int, max_seq_len: int) -> BufferCache:
+        """The cache of this model: a whole-sequence ring per attention layer, an fp32 state per lightning layer."""
+        specs = [blk.mix.cache_spec() for blk in self.layers]
+        cache = BufferCache(self.n_layers, max_batch_size, max_seq_len, 0, 0, None, layer_specs=specs)
+        cache.to(device=self.device, dtype=self.dtype)
+        cache.reset()
+        return cache
+
+    # ------------------------------------------------------------------ forward
+    def _check_runnable(self) -> None:
+        if self.device.type != "cuda":
+            raise _abi.Mb200Error(f"layered decoders run on CUDA only (got {self.device}); no fallback exists")
+        _h.dt_of(self.dtype)
+
+    @torch.inference_mode()
+    def hidden(self, input_ids: torch.Tensor, seqlens: List[int], cache: Optional[BufferCache]) -> torch.Tensor:
+        """The fp32 residual stream [T, width] after the last layer.  Advances the cache.  Without a cache every sequence
+        is taken as whole, from position 0."""
+        self._check_runnable()
+        (num_toks,) = input_ids.shape
+        assert sum(seqlens) == num_toks, (sum(seqlens), num_toks)
+        if cache is None:
+            cache = self.make_cache(len(seqlens), max(seqlens))
+        md = cache.get_input_metadata(seqlens)
+        past = cache._kv_seqlens_host or [0] * len(seqlens)
+        assert max(p + s for p, s in zip(past, seqlens)) <= cache.max_seq_len, "sequence longer than the cache"
+        x = _h.embed_scale(input_ids, self.embed, self.args.embedding_scale)
+        ctx: Dict[str, torch.Tensor] = {}
+        for i, blk in enumerate(self.layers):
+            blk(x, cache.get_view(i, md[i]), ctx)
+            if self._tap is not None:
+                self._tap(i, x)
+        cache.update_seqlens(seqlens)
+        return x
+
+    _tap = None  # debugging hook: called with (layer, residual stream) after every layer
+
+    def logits_of(self, x32: torch.Tensor) -> torch.Tensor:
+        """Final norm + head, fp32 [rows, vocab]."""
+        return _h.linear(_h.rmsnorm(x32, self.final_norm, self.args.norm_eps), self.head, epi=_h.EPI_F32)
+
+    @torch.inference_mode()
+    def forward(self, input_ids: torch.Tensor, seqlens: List[int], cache: Optional[BufferCache] = None,
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """fp32 logits [T, vocab] of a ragged batch (or of the flattened token places `rows` only)."""
+        x = self.hidden(input_ids, seqlens, cache)
+        self.last_argmax = None
+        return self.logits_of(x if rows is None else x.index_select(0, rows))
+
+    # ------------------------------------------------------------------ generate() support
+    def last_argmax_valid_for(self, logits: torch.Tensor) -> bool:
+        return False
+
+    @torch.inference_mode()
+    def next_token_logits(self, tokens: torch.Tensor, cache: BufferCache) -> torch.Tensor:
+        return self.forward(tokens.reshape(-1), [1] * tokens.numel(), cache)
+
+    @torch.inference_mode()
+    def forward_logprobs(self, input_ids: torch.Tensor, seqlens: List[int], cache: Optional[BufferCache],
+                         targets: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """One prompt chunk for generate(): (log-probability of targets[t] at every place with targets[t] >= 0, logits of each
+        sequence's last token)."""
+        logits = self.forward(input_ids, seqlens, cache)
+        lp = _abi.logprob_gather(logits, targets)
+        last_idx = torch.tensor(seqlens, device=input_ids.device).cumsum(0) - 1
+        return lp, logits.index_select(0, last_idx)
+
+    # ------------------------------------------------------------------ weights
+    def _assign(self, k: str, v: torch.Tensor) -> None:
+        def put(dst: torch.Tensor) -> None:
+            assert dst.shape == v.shape, f"{k}: shape {tuple(v.shape)} != expected {tuple(dst.shape)}"
+            dst.copy_(v)
+
+        if k == "embed":
+            return put(self.embed)
+        if k == "final.norm":
+            return put(self.final_norm)
+        if k == "head":
+            return put(self.head)
+        lid, rest = k.split(".", 1)
+        assert lid[0] == "l" and lid[1:].isdigit() and int(lid[1:]) < self.n_layers, f"Unexpected key {k}"
+        blk: LayeredBlock = self.layers[int(lid[1:])]  # type: ignore[assignment]
+        if rest == "norm1":
+            return put(blk.norm1)
+        if rest == "norm2" and blk.norm2 is not None:
+            return put(blk.norm2)
+        part, name = rest.split(".", 1)
+        if part == "mlp" and blk.mlp is not None:
+            ff = blk.mlp
+            if name == "gate":
+                return put(ff.w13.view(ff.a.ff, 2, ff.width)[:, 0])
+            if name == "up":
+                return put(ff.w13.view(ff.a.ff, 2, ff.width)[:, 1])
+            if name == "down":
+                return put(ff.w2)
+        m = blk.mix
+        if part == "mix" and isinstance(m, BiasedAttention):
+            spans = {"q": (0, m.nq), "k": (m.nq, m.nq + m.nk), "v": (m.nq + m.nk, m.nq + m.nk + m.nv)}
+            if name in spans:
+                return put(m.wqkv[spans[name][0]: spans[name][1]])
+            if name.endswith(".b") and name[:-2] in spans:
+                return put(m.bqkv[spans[name[:-2]][0]: spans[name[:-2]][1]])
+            if name == "rel":  # the table's row count comes with the checkpoint
+                m.rel = nn.Parameter(torch.empty(v.shape, dtype=m.rel.dtype, device=m.rel.device), requires_grad=False)
+                m._bias_tab = None
+            direct = {"q.norm": "q_norm", "k.norm": "k_norm", "rel": "rel", "vmix": "vmix", "o": "wo"}
+            if name in direct:
+                return put(getattr(m, direct[name]))
+        if part == "mix" and isinstance(m, LightningMixer):
+            o = [0, m.nqk, 2 * m.nqk, 2 * m.nqk + m.nv, 2 * m.nqk + 2 * m.nv]
+            idx = {"q": 0, "k": 1, "v": 2, "g": 3}
+            if name in idx:
+                return put(m.wqkvg[o[idx[name]]: o[idx[name] + 1]])
+            if name == "norm":
+                return put(m.norm)
+            if name == "o":
+                return put(m.wo)
+        raise ValueError(f"Unexpected key {k}")
+
+    def checkpoint_keys(self) -> List[str]:
+        keys = ["embed", "final.norm", "head"]
+        for i, blk in enumerate(self.layers):
+            p = f"l{i}."
+            keys.append(p + "norm1")
+            if isinstance(blk.mix, BiasedAttention):
+                keys += [p + "mix." + n for n in ("q", "q.b", "k", "k.b", "v", "v.b", "q.norm", "k.norm", "rel", "vmix", "o")]
+            else:
+                keys += [p + "mix." + n for n in ("q", "k", "v", "g", "norm", "o")]
+            if blk.mlp is not None:
+                keys += [p + "norm2", p + "mlp.gate", p + "mlp.up", p + "mlp.down"]
+        return keys
+
+    def load_state_dict(self, state_dict: Any, strict: bool = True, assign: bool = False) -> None:  # type: ignore[override]
+        """Takes checkpoint-keyed tensors and packs them."""
+        del assign
+        with torch.no_grad():
+            for k, v in state_dict.items():
+                self._assign(k, v)
+        if strict:
+            missing = set(self.checkpoint_keys()) - set(state_dict.keys())
+            assert not missing, f"missing keys: {sorted(missing)[:8]}"
+
+    @staticmethod
+    def empty(args: LayeredArgs, device: Union[torch.device, str] = "cuda", dtype: torch.dtype = torch.bfloat16, **kwargs: Any) -> "LayeredTransformer":
+        dev = torch.device(device)
+        if dev.type == "cuda" and dev.index is None:
+            dev = torch.device("cuda", torch.cuda.current_device())
+        with torch.device("meta"):
+            m = LayeredTransformer(args, **kwargs)
+        m = m.to(dtype=dtype).to_empty(device=dev)
+        for blk, L in zip(m.layers, args.layers):  # non-persistent buffers do not survive to_empty
+            if isinstance(blk.mix, LightningMixer):
+                blk.mix.decay = torch.tensor(L.mixer.decay, dtype=torch.float32, device=dev)
+        return m
+
+    @staticmethod
+    def from_folder(folder: Union[Path, str], max_batch_size: int = 1, num_pipeline_ranks: int = 1, device: Union[torch.device, str] = "cuda",
+                    dtype: Optional[torch.dtype] = None, softmax_fp32: bool = True, **kwargs: Any) -> "LayeredTransformer":
+        assert num_pipeline_ranks == 1 and not kwargs, "layered decoders run on one GPU"
+        import safetensors
+
+        with open(Path(folder) / "config.json", "r") as f:
+            args = LayeredArgs.from_dict(json.load(f))
+        args.max_batch_size = max_batch_size
+        with safetensors.safe_open(str(Path(folder) / "model.safetensors"), framework="pt", device="cpu") as f:
+            keys = list(f.keys())
+            model = LayeredTransformer.empty(args, device, dtype or f.get_tensor("final.norm").dtype, softmax_fp32=softmax_fp32)
+            with torch.no_grad():
+                for k in keys:
+                    model._assign(k, f.get_tensor(k))
+            missing = set(model.checkpoint_keys()) - set(keys)
+            assert not missing, f"missing keys: {sorted(missing)[:8]}"
+        return model.eval()

@@ -134,6 +134,13 @@ class Transformer(nn.Module):
             self._ws_tokens = num_tokens
         return self._ws
 
+    def make_cache(self, max_batch_size: int, max_seq_len: int) -> BufferCache:
+        """The cache of this model on its device: one ring per local layer, sized like the reference's (generate.py:68-78)."""
+        cache = BufferCache(self.n_local_layers, max_batch_size, max_seq_len, self.args.n_kv_heads, self.args.head_dim, self.args.sliding_window)
+        cache.to(device=self.device, dtype=self.dtype)
+        cache.reset()
+        return cache
+
     # ------------------------------------------------------------------ forward
     def _check_runnable(self) -> None:
         if self.device.type != "cuda" or self.dtype != torch.bfloat16:

@@ -6,7 +6,7 @@ include/mistral_b200.h); weights are stored pre-packed for the fused kernels:
   FeedForward.w13 [2 * hidden, dim], row 2i = w1[i], row 2i+1 = w3[i]  (SiLU*mul in the epilogue)
 `wq/wk/wv/w1/w3` are exposed as zero-copy views for state-dict compatibility.
 """
-from typing import Optional, Tuple
+from typing import List, Optional, Tuple
 
 import torch
 from torch import nn
@@ -181,3 +181,141 @@ class TransformerBlock(nn.Module):
             hn = _abi.rmsnorm(h, self.ffn_norm.weight, self.norm_eps)
             return self.feed_forward.run(hn, h, ws)  # router + grouped experts + ordered combine + residual, no host sync
         return self.feed_forward.run(h, self.ffn_norm.weight, self.norm_eps, h, ws)
+
+
+# ============================================================================= layered decoders
+# Mixers and feed-forward of models described layer by layer (args.LayeredArgs).  They run on libmb200_hybrid
+# (include/mistral_b200_hybrid.h): the residual stream `x32` is fp32 and updated in place by the epilogue of each
+# sublayer's last Linear; activations and weights are stored in the model dtype (bf16 or fp32).
+import math  # noqa: E402
+from typing import Dict  # noqa: E402
+
+from . import _abi_hybrid as _h  # noqa: E402
+from .args import BiasedAttentionArgs, ClampedGluArgs, LightningArgs  # noqa: E402
+from .cache import LayerCacheSpec  # noqa: E402
+
+
+def distance_buckets(rows: int, far: float) -> List[int]:
+    """bucket(n) for n = 0 .. n_sat, where n_sat is the first distance in the last bucket: one row per distance below rows/2,
+    then (rows - rows/2) logarithmic steps up to `far`.  Evaluated in double precision on the host, once per layer."""
+    half = rows // 2
+    assert far > half > 0, "the logarithmic part of the distance bias needs bias_max > rows / 2"
+    out: List[int] = []
+    n = 0
+    while True:
+        b = n if n < half else min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
+        out.append(b)
+        if b == rows - 1:
+            return out
+        n += 1
+
+
+class BiasedAttention(nn.Module):
+    """Causal softmax attention with per-head q/k RMS norm, position-dependent query temperature, learned distance bias and
+    optional value mixing.  Packed weights: wqkv = q ++ k ++ v rows (+ bqkv), like `Attention.wqkv`."""
+
+    def __init__(self, width: int, a: BiasedAttentionArgs, eps: float, first_vmix: bool, rel_rows: int = 0):
+        super().__init__()
+        self.a, self.eps, self.first_vmix = a, eps, first_vmix
+        self.nq, self.nk, self.nv = a.heads * a.dim, a.kv_heads * a.dim, a.kv_heads * a.vdim
+        n = self.nq + self.nk + self.nv
+        self.wqkv = nn.Parameter(torch.empty(n, width), requires_grad=False)
+        self.bqkv = nn.Parameter(torch.empty(n), requires_grad=False)
+        self.q_norm = nn.Parameter(torch.empty(a.dim), requires_grad=False)
+        self.k_norm = nn.Parameter(torch.empty(a.dim), requires_grad=False)
+        self.rel = nn.Parameter(torch.empty(max(rel_rows, 2), a.heads), requires_grad=False)  # resized by the loader to the checkpoint's rows
+        self.vmix = nn.Parameter(torch.empty(()), requires_grad=False)
+        self.wo = nn.Parameter(torch.empty(width, a.heads * a.vdim), requires_grad=False)
+        self._bias_tab: Optional[torch.Tensor] = None
+
+    def cache_spec(self) -> LayerCacheSpec:
+        return LayerCacheSpec(kind="ring", n_kv_heads=self.a.kv_heads, k_dim=self.a.dim, v_dim=self.a.vdim, window=None)
+
+    def bias_table(self) -> torch.Tensor:
+        """fp32 [n_sat + 1, heads]: the bias of every distance up to the first one of the last bucket (larger ones share it)."""
+        if self._bias_tab is None or self._bias_tab.device != self.rel.device:
+            idx = torch.tensor(distance_buckets(self.rel.shape[0], self.a.bias_max), device=self.rel.device)
+            self._bias_tab = self.rel.float().index_select(0, idx).contiguous()
+        return self._bias_tab
+
+    def run(self, hn: torch.Tensor, x32: torch.Tensor, view: CacheView, ctx: Dict[str, torch.Tensor]) -> None:
+        a, md = self.a, view.metadata
+        T = hn.shape[0]
+        qkv = _h.linear(hn, self.wqkv, self.bqkv)
+        q = torch.empty(T, self.nq, dtype=hn.dtype, device=hn.device)
+        mode = 0
+        if a.v_mix:
+            if self.first_vmix:
+                ctx["v_first"] = torch.empty(T, self.nv, dtype=hn.dtype, device=hn.device)
+                mode = 1
+            else:
+                assert ctx["v_first"].shape[1] == self.nv, "value mixing needs equal value sizes in the mixed layers"
+                mode = 2
+        _h.attn_prep(qkv, self.q_norm, self.k_norm, md.positions, md.cache_rows, q, view.cache_k, view.cache_v, ctx.get("v_first"), self.vmix, mode,
+                     a.heads, a.kv_heads, a.dim, a.vdim, self.eps, a.temp_coef, a.temp_every)
+        out = torch.empty(T, a.heads * a.vdim, dtype=hn.dtype, device=hn.device)
+        _h.attn_bias(q, view.cache_k, view.cache_v, self.bias_table(), md.positions, md.q_start, md.slots, out, len(md.seqlens), md.window,
+                     a.heads, a.kv_heads, a.dim, a.vdim, a.scale)
+        _h.linear(out, self.wo, epi=_h.EPI_RESIDUAL, residual=x32)
+
+
+class LightningMixer(nn.Module):
+    """Linear attention with a fixed per-head decay: S <- decay S + k v^T, o = S^T q (fp32 state in the cache), all heads RMS-normed
+    together, gated by sigmoid(W_g h).  Packed weights: wqkvg = q ++ k ++ v ++ g rows; SiLU on q, k, v in the Linear's epilogue."""
+
+    def __init__(self, width: int, a: LightningArgs, eps: float):
+        super().__init__()
+        self.a, self.eps = a, eps
+        self.nqk, self.nv = a.heads * a.dim, a.heads * a.vdim
+        self.wqkvg = nn.Parameter(torch.empty(2 * self.nqk + 2 * self.nv, width), requires_grad=False)
+        self.norm = nn.Parameter(torch.empty(self.nv), requires_grad=False)
+        self.wo = nn.Parameter(torch.empty(width, self.nv), requires_grad=False)
+        self.register_buffer("decay", torch.tensor(a.decay, dtype=torch.float32), persistent=False)
+
+    def cache_spec(self) -> LayerCacheSpec:
+        return LayerCacheSpec(kind="state", state_shape=(self.a.heads, self.a.dim, self.a.vdim))
+
+    def run(self, hn: torch.Tensor, x32: torch.Tensor, view: CacheView, ctx: Dict[str, torch.Tensor]) -> None:
+        a, md = self.a, view.metadata
+        T = hn.shape[0]
+        qkvg = _h.linear(hn, self.wqkvg, n_act=2 * self.nqk + self.nv)
+        o32 = torch.empty(T, self.nv, dtype=torch.float32, device=hn.device)
+        _h.lightning_scan(qkvg, view.state, self.decay.float(), md.q_start, md.seqpos, md.slots, o32, len(md.seqlens), a.heads, a.dim, a.vdim)
+        y = _h.gated_headnorm(o32, self.norm, qkvg, qkvg.shape[1], 2 * self.nqk + self.nv, self.eps)
+        _h.linear(y, self.wo, epi=_h.EPI_RESIDUAL, residual=x32)
+
+
+class ClampedGLU(nn.Module):
+    """Feed-forward with clamped gate and up projections (args.ClampedGluArgs).  w13 interleaves gate and up rows like
+    `FeedForward.w13`, so the activation is the epilogue of one Linear."""
+
+    def __init__(self, width: int, a: ClampedGluArgs):
+        super().__init__()
+        self.a, self.width = a, width
+        self.w13 = nn.Parameter(torch.empty(2 * a.ff, width), requires_grad=False)
+        self.w2 = nn.Parameter(torch.empty(width, a.ff), requires_grad=False)
+
+    def run(self, hn: torch.Tensor, x32: torch.Tensor) -> None:
+        y = _h.linear(hn, self.w13, epi=_h.EPI_GLU, limit=self.a.limit, alpha=self.a.alpha)
+        _h.linear(y, self.w2, epi=_h.EPI_RESIDUAL, residual=x32)
+
+
+MIXERS = {"attention": BiasedAttention, "lightning": LightningMixer}
+
+
+class LayeredBlock(nn.Module):
+    """x <- x + mixer(norm1(x)); x <- x + ff(norm2(x)) when the layer has a feed-forward.  `x32` is updated in place."""
+
+    def __init__(self, width: int, eps: float, mixer: nn.Module, mlp: Optional[ClampedGLU], dtype_probe: str = "norm1"):
+        super().__init__()
+        self.eps = eps
+        self.norm1 = nn.Parameter(torch.empty(width), requires_grad=False)
+        self.mix = mixer
+        self.mlp = mlp
+        self.norm2 = nn.Parameter(torch.empty(width), requires_grad=False) if mlp is not None else None
+
+    def forward(self, x32: torch.Tensor, view: CacheView, ctx: Dict[str, torch.Tensor]) -> torch.Tensor:
+        self.mix.run(_h.rmsnorm(x32, self.norm1, self.eps), x32, view, ctx)
+        if self.mlp is not None:
+            self.mlp.run(_h.rmsnorm(x32, self.norm2, self.eps), x32)
+        return x32
