@@ -588,12 +588,18 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--no-sharded", action="store_true")
+    ap.add_argument("--design", default=None, choices=["fesenex"],
+                    help="instead of the default workload: the layered decoder beside the dense transformer of equal size (bench_layered.py)")
     a = ap.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    if a.impl == "reference":
+    if a.design is not None:
+        import bench_layered
+        torch.cuda.set_device(local)
+        out = bench_layered.run(a, measured_peaks()) if rank == 0 else None
+    elif a.impl == "reference":
         out = run_reference(a, rank, world)
     else:
         torch.cuda.set_device(local)

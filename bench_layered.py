@@ -1,0 +1,181 @@
+"""`bench.py --design fesenex`: prefill and decode throughput of the layered decoder at layer sizes of real models (random
+weights), beside the dense `Transformer` of equal width / heads / feed-forward size / depth / vocabulary, plus the time of each
+hybrid kernel at those shapes against its roofline (bf16 tensor peak or HBM copy bandwidth from MEASURED_PEAKS.json).
+Timed with CUDA events after warm-up; the prompt batch and the weights exceed L2 at the larger size, and L2 is flushed between
+timed kernel launches.  Prints one JSON line."""
+import json
+import math
+import time
+
+import torch
+
+SIZES = {
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=8192, vocab=32768, layers=8, lin_heads=16),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=14336, vocab=32768, layers=4, lin_heads=32),
+}
+
+
+def layered_config(s: dict) -> dict:
+    att = {"type": "attention", "mixer": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "scale": s["dim"] ** -0.5,
+                                          "bias_max": 4096, "q_temp": {"coef": 0.1, "every": 1024}, "v_mix": True},
+           "mlp": {"kind": "dense", "ff": s["ff"], "limit": 7.0}}
+    lin = {"type": "lightning", "mixer": {"heads": s["lin_heads"], "dim": s["dim"], "vdim": s["dim"],
+                                          "decay": [math.exp(-1.0 / (4 + 8 * h)) for h in range(s["lin_heads"])]},
+           "mlp": {"kind": "dense", "ff": s["ff"], "limit": 7.0}}
+    return {"architecture": "Fesenex", "vocab": s["vocab"], "width": s["width"], "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5},
+            "layers": [lin if i % 4 == 3 else att for i in range(s["layers"])]}
+
+
+def build_layered(s: dict, dev):
+    from mistral_inference_b200.args import LayeredArgs
+    from mistral_inference_b200.layered import LayeredTransformer
+    from mistral_inference_b200.transformer_layers import BiasedAttention
+
+    m = LayeredTransformer.empty(LayeredArgs.from_dict(layered_config(s)), dev, torch.bfloat16)
+    g = torch.Generator(device=dev).manual_seed(0)
+    with torch.no_grad():
+        for blk in m.layers:
+            if isinstance(blk.mix, BiasedAttention):
+                blk.mix.rel = torch.nn.Parameter(torch.empty(32, blk.mix.a.heads, dtype=torch.bfloat16, device=dev), requires_grad=False)
+        for n, p in m.named_parameters():
+            if p.dim() >= 2:
+                p.copy_(torch.randn(p.shape, generator=g, device=dev, dtype=torch.float32) / math.sqrt(p.shape[-1]))
+            elif "norm" in n:
+                p.fill_(1.0)
+            else:
+                p.copy_(torch.randn(p.shape, generator=g, device=dev, dtype=torch.float32) * 0.1)
+    return m.eval()
+
+
+def build_dense(s: dict, dev):
+    import mistral_inference_b200 as mi
+    from mistral_inference_b200.transformer import Transformer
+
+    args = mi.TransformerArgs(dim=s["width"], n_layers=s["layers"], head_dim=s["dim"], hidden_dim=s["ff"], n_heads=s["heads"], n_kv_heads=s["kv_heads"],
+                              norm_eps=1e-5, vocab_size=s["vocab"], max_batch_size=8)
+    m = Transformer.empty(args, dev, torch.bfloat16)
+    g = torch.Generator(device=dev).manual_seed(0)
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if p.dim() >= 2:
+                p.copy_(torch.randn(p.shape, generator=g, device=dev, dtype=torch.float32) / math.sqrt(p.shape[-1]))
+            else:
+                p.fill_(1.0)
+    return m.eval()
+
+
+def _time(fn, warmup: int, steps: int, flush=None) -> float:
+    """Median milliseconds of fn() over `steps` runs."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(steps):
+        if flush is not None:
+            flush.add_(1.0)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def end_to_end(model, vocab: int, T: int, ctx: int, batches, warmup: int, steps: int, dev) -> dict:
+    out = {}
+    ids = torch.randint(0, vocab, (T,), device=dev)
+    cache = model.make_cache(max(batches), ctx + 64 + warmup + steps)
+
+    def prefill():
+        cache.reset()
+        model.forward(ids, [T], cache)
+
+    ms = _time(prefill, max(3, warmup // 4), max(3, steps // 8))
+    out["prefill"] = {"tokens": T, "ms": round(ms, 3), "tok_s": round(T / ms * 1e3, 1)}
+    for B in batches:
+        cache.reset()
+        n = ctx // 2 if B > 1 else ctx
+        model.forward(ids[:n].repeat(B), [n] * B, cache)
+        tok = torch.randint(0, vocab, (B,), device=dev)
+        ms = _time(lambda: model.next_token_logits(tok, cache), warmup, steps)
+        out[f"decode_b{B}"] = {"context": n, "ms": round(ms, 4), "tok_s": round(B / ms * 1e3, 1)}
+    return out
+
+
+def kernel_table(s: dict, T: int, ctx: int, peaks: dict, dev) -> dict:
+    """Every hybrid kernel alone at this size: time, achieved rate, fraction of the measured roofline."""
+    from mistral_inference_b200 import _abi_hybrid as h
+
+    bf = torch.bfloat16
+    W, H, G, d, ff = s["width"], s["heads"], s["kv_heads"], s["dim"], s["ff"]
+    flush = torch.zeros(160 << 20, dtype=torch.float32, device=dev)  # 640 MB > L2
+    rows = {}
+
+    def rec(name, ms, flops=0.0, bytes_=0.0):
+        r = {"ms": round(ms, 4)}
+        if flops:
+            r["tflops"] = round(flops / ms / 1e9, 1)
+            r["of_bf16_peak"] = round(flops / ms / 1e9 / peaks["bf16_tflops"], 3)
+        if bytes_:
+            r["gb_s"] = round(bytes_ / ms / 1e6, 1)
+            r["of_hbm_peak"] = round(bytes_ / ms / 1e6 / peaks["hbm_gbs"], 3)
+        rows[name] = r
+
+    x = torch.randn(T, W, device=dev).to(bf)
+    w13 = torch.randn(2 * ff, W, device=dev).to(bf) * 0.02
+    rec("linear_tiled_mma gate/up+glu", _time(lambda: h.linear(x, w13, epi=h.EPI_GLU, limit=7.0, alpha=1.702), 3, 8, flush), flops=2.0 * T * 2 * ff * W)
+    for M in (1, 8):
+        xs = x[:M].contiguous()
+        rec(f"linear_skinny gate/up+glu M={M}", _time(lambda: h.linear(xs, w13, epi=h.EPI_GLU, limit=7.0, alpha=1.702), 3, 8, flush), bytes_=w13.numel() * 2.0)
+    # attention: a prompt of T tokens, then one token per sequence at context ctx
+    from mistral_inference_b200.cache import BufferCache, LayerCacheSpec
+    B = 8
+    cache = BufferCache(1, B, ctx + 8, 0, 0, None, layer_specs=[LayerCacheSpec(kind="ring", n_kv_heads=G, k_dim=d, v_dim=d)]).to(dev, bf)
+    cache.cache_k[0].normal_(); cache.cache_v[0].normal_()
+    tab = torch.zeros(64, H, device=dev)
+    md = cache.get_input_metadata([T])[0]
+    q = torch.randn(T, H * d, device=dev).to(bf)
+    o = torch.empty_like(q)
+    att = lambda: h.attn_bias(q, cache.cache_k[0], cache.cache_v[0], tab, md.positions, md.q_start, md.slots, o, 1, ctx + 8, H, G, d, d, d ** -0.5,
+                              n_tiles=(T + 63) // 64)  # noqa: E731
+    rec("attn_bias_flash prompt", _time(att, 2, 5, flush), flops=4.0 * d * H * T * (T + 1) / 2)
+    cache.reset(); cache.init_kvseqlens(B); cache.update_seqlens([ctx] * B)
+    md2 = cache.get_input_metadata([1] * B)[0]
+    q2, o2 = q[:B].contiguous(), torch.empty(B, H * d, device=dev, dtype=bf)
+    dec = lambda: h.attn_bias(q2, cache.cache_k[0], cache.cache_v[0], tab, md2.positions, md2.q_start, md2.slots, o2, B, ctx + 8, H, G, d, d, d ** -0.5,
+                              splits=h.attn_splits(B, H, ctx + 8))  # noqa: E731
+    rec(f"attn_bias decode B={B} ctx={ctx}", _time(dec, 3, 8, flush), bytes_=2.0 * B * (ctx + 1) * G * d * 2)
+    # lightning: prompt and decode
+    LH = s["lin_heads"]
+    qkvg = torch.randn(T, 4 * LH * d, device=dev).to(bf) * 0.1
+    state = torch.zeros(B, LH, d, d, device=dev)
+    dec_ = torch.full((LH,), 0.97, device=dev)
+    o32 = torch.empty(T, LH * d, device=dev)
+    zero = torch.zeros(1, dtype=torch.int32, device=dev)
+    rec("lightning_scan prompt", _time(lambda: h.lightning_scan(qkvg, state, dec_, md.q_start, zero, md.slots, o32, 1, LH, d, d), 2, 5, flush),
+        flops=4.0 * T * LH * d * d)
+    one = torch.ones(B, dtype=torch.int32, device=dev)
+    rec(f"lightning_scan decode B={B}", _time(lambda: h.lightning_scan(qkvg, state, dec_, md2.q_start, one, md2.slots, o32, B, LH, d, d), 3, 8, flush),
+        bytes_=2.0 * state.numel() * 4)
+    return rows
+
+
+def run(a, peaks: dict) -> dict:
+    dev = torch.device("cuda", torch.cuda.current_device())
+    T, ctx = a.prefill, a.prefill
+    res = {"design": "Fesenex", "dtype": "bf16", "data": "synthetic", "prompt_tokens": T, "peaks": {k: peaks.get(k) for k in ("hbm_gbs", "bf16_tflops")}, "sizes": {}}
+    for name, s in SIZES.items():
+        t0 = time.time()
+        m = build_layered(s, dev)
+        new = end_to_end(m, s["vocab"], T, ctx, (1, 8), a.warmup, a.steps, dev)
+        del m
+        torch.cuda.empty_cache()
+        d = build_dense(s, dev)
+        old = end_to_end(d, s["vocab"], T, ctx, (1, 8), a.warmup, a.steps, dev)
+        del d
+        torch.cuda.empty_cache()
+        res["sizes"][name] = {"config": s, "layered": new, "dense_transformer": old, "kernels": kernel_table(s, T, ctx, peaks, dev),
+                              "seconds": round(time.time() - t0, 1)}
+    return res

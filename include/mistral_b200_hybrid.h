@@ -44,10 +44,13 @@ int mbh_attn_prep(const void* qkv, const void* qnorm, const void* knorm, const v
 
 /* Causal softmax attention of q[T, H*d] over the ring: token t of sequence b (q_start[B+1]) at position positions[t] sees keys
  * 0..position of cache block slots[b] (W rows each, key j in row j % W); score = q.k * scale + bias_tab[min(distance, n_tab-1), h]
- * (fp32 [n_tab, H]).  out [T, H*e]. */
+ * (fp32 [n_tab, H]).  out [T, H*e].
+ * n_tiles > 0 (prompts): the number of 64-query tiles, sum over sequences of ceil(len / 64); with bf16 storage and key/value
+ * sizes among {32, 64, 128} the tensor-core kernel runs (P rounded to bf16 before P V).  n_tiles = 0: the exact fp32 kernel,
+ * with `splits` > 1 CTAs per (token, head) along the keys (decode) and their partial results in scratch (fp32 [T*H, splits, 2 + e]). */
 int mbh_attn_bias(const void* q, const void* cache_k, const void* cache_v, const void* bias_tab, int64_t n_tab, const void* positions,
                   const void* q_start, const void* slots, void* out, int64_t T, int64_t B, int64_t W, int64_t H, int64_t G, int64_t d, int64_t e,
-                  float scale, int dt, void* stream);
+                  float scale, int64_t n_tiles, int64_t splits, void* scratch, int dt, void* stream);
 
 /* Decayed linear attention.  qkvg [T, 2*H*d + 2*H*e] = q | k | v | gate; per head S <- decay[h] S + k v^T, o = S^T q, fp32;
  * state fp32 [slots, H, d, e] is read (unless seqpos[b] == 0: starts at zero) and written back; o32 fp32 [T, H*e]. */

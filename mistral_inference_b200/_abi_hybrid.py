@@ -25,7 +25,7 @@ _SIGNATURES = {
     "mbh_rmsnorm": (c_int, [P, P, P, I, I, F, c_int, P]),
     "mbh_linear": (c_int, [P, P, P, P, P, I, I, I, c_int, I, F, F, c_int, P]),
     "mbh_attn_prep": (c_int, [P, P, P, P, P, P, P, P, P, P, c_int, I, I, I, I, I, F, F, I, c_int, P]),
-    "mbh_attn_bias": (c_int, [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, c_int, P]),
+    "mbh_attn_bias": (c_int, [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, c_int, P]),
     "mbh_lightning_scan": (c_int, [P, P, P, P, P, P, P, I, I, I, I, c_int, P]),
     "mbh_gated_headnorm": (c_int, [P, P, P, I, I, P, I, I, F, c_int, P]),
 }
@@ -111,10 +111,19 @@ def attn_prep(qkv, qnorm, knorm, positions, cache_rows, q_out, cache_k, cache_v,
                                _stream()), "mbh_attn_prep")
 
 
-def attn_bias(q, cache_k, cache_v, bias_tab, positions, q_start, slots, out, B: int, W: int, H: int, G: int, d: int, e: int, scale: float) -> None:
+def attn_bias(q, cache_k, cache_v, bias_tab, positions, q_start, slots, out, B: int, W: int, H: int, G: int, d: int, e: int, scale: float,
+              n_tiles: int = 0, splits: int = 1) -> None:
+    """n_tiles = sum over sequences of ceil(len / 64) selects the tensor-core prompt kernel (bf16); 0 the exact fp32 one."""
     assert bias_tab.dtype == torch.float32 and bias_tab.shape[1] == H
+    scratch = torch.empty(q.shape[0] * H * splits * (2 + e), dtype=torch.float32, device=q.device) if splits > 1 and n_tiles == 0 else None
     _check(lib().mbh_attn_bias(_ptr(q), _ptr(cache_k), _ptr(cache_v), _ptr(bias_tab), bias_tab.shape[0], _ptr(positions), _ptr(q_start), _ptr(slots),
-                               _ptr(out), q.shape[0], B, W, H, G, d, e, scale, dt_of(q.dtype), _stream()), "mbh_attn_bias")
+                               _ptr(out), q.shape[0], B, W, H, G, d, e, scale, n_tiles, splits, _ptr(scratch), dt_of(q.dtype), _stream()), "mbh_attn_bias")
+
+
+def attn_splits(T: int, H: int, W: int, n_sm: int = 148) -> int:
+    """CTAs per (token, head) along the keys: enough to fill two CTAs per SM, at most one per 512 ring rows (a function of the
+    batch and the ring only, so that a captured decode graph stays valid as the context grows)."""
+    return int(max(1, min((2 * n_sm + T * H - 1) // (T * H), (W + 511) // 512, 32)))
 
 
 def lightning_scan(qkvg, state, decay, q_start, seqpos, slots, o32, B: int, H: int, d: int, e: int) -> None:

@@ -153,6 +153,7 @@ class BufferCache:
         """Sequences `indices` (places in the current batch order) have ended: what they hold is given back, the others keep
         their rows and their order.  The next `reset()` + batch hands every row out again."""
         assert self._kv_seqlens_host is not None
+        assert self.layer_specs is not None, "retiring from a running batch needs kernels that address rows by slot (layered models)"
         gone = set(indices)
         assert all(0 <= i < len(self._kv_seqlens_host) for i in gone), indices
         rows = self.rows
@@ -211,7 +212,9 @@ class BufferCache:
         positions = seqpos[batch_idx] + local
         distinct = sorted(set(self.cache_sizes))
         slot = np.asarray(self.rows, dtype=np.int64)
-        total = T + (B + 1) + B + len(distinct) * (T + B) + B
+        with_slots = self.layer_specs is not None  # kernels of layered models take the row block of each sequence
+        assert with_slots or self.rows == list(range(B)), "this model's kernels address sequence b at row block b"
+        total = T + (B + 1) + B + len(distinct) * (T + B) + (B if with_slots else 0)
         host = np.empty(total, dtype=np.int32)
         layout = {"T": T, "B": B, "prefill": first_prefill or subsequent_prefill, "first_prefill": first_prefill, "max_seqlen": int(sl.max()), "windows": distinct}
         o = 0
@@ -223,8 +226,9 @@ class BufferCache:
             rows = np.where(cached, positions % W + slot[batch_idx] * W, -1)
             host[o:o + T] = rows; o += T
             host[o:o + B] = np.minimum(seqpos + np.minimum(sl, W), W); o += B
-        host[o:o + B] = slot; o += B
-        layout["slots"] = True
+        if with_slots:
+            host[o:o + B] = slot; o += B
+        layout["slots"] = with_slots
         return host, layout
 
     def metadata_from_block(self, dev: torch.Tensor, layout: dict, seqlens: List[int]) -> List[CacheInputMetadata]:

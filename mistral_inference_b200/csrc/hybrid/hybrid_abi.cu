@@ -3,6 +3,7 @@
 // 0 = bf16, 1 = fp32.  Every call returns 0 or a CUDA error code; mbh_last_error() gives the text.
 #include "hybrid_linear.cuh"
 #include "hybrid_mixers.cuh"
+#include "hybrid_attn_flash.cuh"
 #include "../../../include/mistral_b200_hybrid.h"
 
 #include <stdio.h>
@@ -45,7 +46,8 @@ template <typename T> static void run_rmsnorm(const void* x32, const void* w, vo
 }
 template <typename T> static void run_prep(const AttnPrepArgs& a, int64_t T_, cudaStream_t st) { attn_prep_kernel<T><<<(unsigned)T_, 128, 0, st>>>(a); }
 template <typename T> static void run_attn(const AttnArgs& a, size_t smem, cudaStream_t st) {
-    attn_bias_kernel<T><<<(unsigned)(a.T * a.H), AT_WARPS * 32, smem, st>>>(a);
+    attn_bias_kernel<T><<<dim3((unsigned)(a.T * a.H), (unsigned)a.splits), AT_WARPS * 32, smem, st>>>(a);
+    if (a.splits > 1) attn_merge_kernel<T><<<(unsigned)(a.T * a.H), 64, 0, st>>>(a.scratch, (T*)a.out, a.splits, a.e);
 }
 template <typename T> static void run_headnorm(const void* o32, const void* w, const void* g, int64_t g_pitch, int64_t g_off, void* y, int64_t T_,
                                                int64_t N, float eps, cudaStream_t st) {
@@ -97,14 +99,19 @@ int mbh_attn_prep(const void* qkv, const void* qnorm, const void* knorm, const v
 
 int mbh_attn_bias(const void* q, const void* cache_k, const void* cache_v, const void* bias_tab, int64_t n_tab, const void* positions,
                   const void* q_start, const void* slots, void* out, int64_t T, int64_t B, int64_t W, int64_t H, int64_t G, int64_t d, int64_t e,
-                  float scale, int dt, void* stream) {
+                  float scale, int64_t n_tiles, int64_t splits, void* scratch, int dt, void* stream) {
     if (T == 0) return 0;
     if (e > 32 * AT_MAXR) return bad("mbh_attn_bias: value size above 256");
     if (H % G) return bad("mbh_attn_bias: heads must be a multiple of kv heads");
     AttnArgs a{q, cache_k, cache_v, (const float*)bias_tab, (int)n_tab, (const int*)positions, (const int*)q_start, (const int*)slots, out,
-               (int)T, (int)B, (int)W, (int)H, (int)G, (int)d, (int)e, scale};
+               (int)T, (int)B, (int)W, (int)H, (int)G, (int)d, (int)e, scale, (int)(splits > 1 && scratch ? splits : 1), (float*)scratch};
     const size_t smem = sizeof(float) * ((size_t)d + AT_WARPS * AT_CHUNK + AT_WARPS * (2 + 32 * AT_MAXR));
     cudaStream_t st = (cudaStream_t)stream;
+    // prompts in bf16: the tensor-core kernel, when the caller counted the 64-query tiles and the sizes are instantiated
+    if (dt == 0 && n_tiles > 0 && launch_attn_flash(a, (int)n_tiles, st)) {
+        cudaError_t ferr = cudaGetLastError();
+        return ferr ? fail(ferr, "mbh_attn_bias (flash)") : 0;
+    }
     DISPATCH(dt, run_attn<ST>(a, smem, st));
     cudaError_t err = cudaGetLastError();
     return err ? fail(err, "mbh_attn_bias") : 0;

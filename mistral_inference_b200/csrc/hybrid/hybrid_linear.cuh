@@ -191,59 +191,122 @@ __global__ void __launch_bounds__(MM_THREADS) linear_tiled_mma(LinearArgs a) {
 // ------------------------------------------------------------------------------------------------ skinny (decode)
 constexpr int SK_MAX_M = 8, SK_WARPS = 8;
 
-template <typename T, int MM>
+// R weight rows per warp (R even: gate/up pairs stay together); more rows per warp = fewer re-reads of x per weight byte
+template <typename T, int MM, int R>
 __global__ void __launch_bounds__(SK_WARPS * 32) linear_skinny(LinearArgs a) {
     const T* X = static_cast<const T*>(a.x);
     const T* W = static_cast<const T*>(a.w);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n = (blockIdx.x * SK_WARPS + warp) * 2;
+    const int n = (blockIdx.x * SK_WARPS + warp) * R;
     if (n >= a.N) return;
-    const bool has1 = n + 1 < a.N;
-    const T* w0 = W + (size_t)n * a.K;
-    const T* w1 = W + (size_t)(has1 ? n + 1 : n) * a.K;
-    float acc0[MM], acc1[MM];
+    const T* wr[R];
 #pragma unroll
-    for (int m = 0; m < MM; ++m) acc0[m] = acc1[m] = 0.f;
+    for (int r = 0; r < R; ++r) wr[r] = W + (size_t)min(n + r, a.N - 1) * a.K;
+    float acc[R][MM];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < MM; ++m) acc[r][m] = 0.f;
     constexpr int V = Vec<T>::N;
     const bool vec_ok = (a.K % V == 0) && ((reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(W)) % 16 == 0);
     if (vec_ok) {
         for (int k = lane * V; k < a.K; k += 32 * V) {
-            float a0[V], a1[V], xv[V];
-            Vec<T>::load(w0 + k, a0);
-            Vec<T>::load(w1 + k, a1);
+            float wv[R][V], xv[V];
+#pragma unroll
+            for (int r = 0; r < R; ++r) Vec<T>::load(wr[r] + k, wv[r]);
 #pragma unroll
             for (int m = 0; m < MM; ++m) {
                 if (m < a.M) {
                     Vec<T>::load(X + (size_t)m * a.K + k, xv);
 #pragma unroll
-                    for (int i = 0; i < V; ++i) { acc0[m] = fmaf(a0[i], xv[i], acc0[m]); acc1[m] = fmaf(a1[i], xv[i], acc1[m]); }
+                    for (int r = 0; r < R; ++r)
+#pragma unroll
+                        for (int i = 0; i < V; ++i) acc[r][m] = fmaf(wv[r][i], xv[i], acc[r][m]);
                 }
             }
         }
     } else {
         for (int k = lane; k < a.K; k += 32) {
-            float a0 = to_f(w0[k]), a1 = to_f(w1[k]);
+            float wv[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) wv[r] = to_f(wr[r][k]);
 #pragma unroll
             for (int m = 0; m < MM; ++m)
-                if (m < a.M) { float xv = to_f(X[(size_t)m * a.K + k]); acc0[m] = fmaf(a0, xv, acc0[m]); acc1[m] = fmaf(a1, xv, acc1[m]); }
+                if (m < a.M) {
+                    const float xv = to_f(X[(size_t)m * a.K + k]);
+#pragma unroll
+                    for (int r = 0; r < R; ++r) acc[r][m] = fmaf(wv[r], xv, acc[r][m]);
+                }
         }
     }
 #pragma unroll
-    for (int m = 0; m < MM; ++m) {
-        float s0 = warp_sum(acc0[m]), s1 = warp_sum(acc1[m]);
-        if (lane == 0 && m < a.M) epilogue_pair<T>(a, m, n, s0, s1, has1);
+    for (int m = 0; m < MM; ++m)
+#pragma unroll
+        for (int r = 0; r < R; r += 2) {
+            const float s0 = warp_sum(acc[r][m]), s1 = warp_sum(acc[r + 1][m]);
+            if (lane == 0 && m < a.M && n + r < a.N) epilogue_pair<T>(a, m, n + r, s0, s1, n + r + 1 < a.N);
+        }
+}
+
+// ------------------------------------------------------------------------------------------------ skinny on tensor cores (bf16, 3..8 rows)
+// y^T = W x^T: the 16 weight rows of a CTA are the M side of m16n8k16 tiles, the (up to 8) tokens the N side, so a decode batch
+// costs one tensor-core instruction per 16 x 16 weights instead of 8 FMAs per weight.  The CTA's warps split K; every lane
+// loads 16 contiguous bytes of two weight rows and of one token's activations per step -- the k order inside a step is
+// permuted identically for both operands, which a dot product does not notice.  Needs K % 8 == 0 and 16-byte aligned rows.
+constexpr int SKM_WARPS = 8;
+
+__global__ void __launch_bounds__(SKM_WARPS * 32) linear_skinny_mma(LinearArgs a) {
+    __shared__ float part[SKM_WARPS][16][9];
+    const bf16* X = static_cast<const bf16*>(a.x);
+    const bf16* W = static_cast<const bf16*>(a.w);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+    const int n0 = blockIdx.x * 16;
+    const bf16* wa = W + (size_t)min(n0 + gid, a.N - 1) * a.K;
+    const bf16* wb = W + (size_t)min(n0 + gid + 8, a.N - 1) * a.K;
+    const bool xrow = gid < a.M;
+    const bf16* xr = X + (size_t)(xrow ? gid : 0) * a.K;
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int kb = warp * 32; kb < a.K; kb += SKM_WARPS * 32) {
+        const int k = kb + tig * 8;
+        uint4 va = make_uint4(0, 0, 0, 0), vb = va, vx = va;
+        if (k < a.K) {
+            va = *reinterpret_cast<const uint4*>(wa + k);
+            vb = *reinterpret_cast<const uint4*>(wb + k);
+            if (xrow) vx = *reinterpret_cast<const uint4*>(xr + k);
+        }
+        const uint32_t a0[4] = {va.x, vb.x, va.y, vb.y}, a1[4] = {va.z, vb.z, va.w, vb.w};
+        mma_bf16(c, a0, vx.x, vx.y);
+        mma_bf16(c, a1, vx.z, vx.w);
+    }
+    part[warp][gid][tig * 2] = c[0]; part[warp][gid][tig * 2 + 1] = c[1];
+    part[warp][gid + 8][tig * 2] = c[2]; part[warp][gid + 8][tig * 2 + 1] = c[3];
+    __syncthreads();
+    if (threadIdx.x < 64) {
+        const int m = threadIdx.x & 7, r = (threadIdx.x >> 3) * 2, n = n0 + r;
+        if (m < a.M && n < a.N) {
+            float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+            for (int w = 0; w < SKM_WARPS; ++w) { s0 += part[w][r][m]; s1 += part[w][r + 1][m]; }
+            epilogue_pair<bf16>(a, m, n, s0, s1, n + 1 < a.N);
+        }
     }
 }
 
 template <typename T>
 inline cudaError_t launch_linear(const LinearArgs& a, cudaStream_t st) {
     if (a.M <= 0 || a.N <= 0) return cudaSuccess;
+    if constexpr (sizeof(T) == 2) {
+        if (a.M > 2 && a.M <= 8 && a.K % 8 == 0 && (reinterpret_cast<uintptr_t>(a.x) | reinterpret_cast<uintptr_t>(a.w)) % 16 == 0) {
+            linear_skinny_mma<<<(a.N + 15) / 16, SKM_WARPS * 32, 0, st>>>(a);
+            return cudaGetLastError();
+        }
+    }
     if (a.M <= SK_MAX_M) {
-        dim3 grid((a.N + 2 * SK_WARPS - 1) / (2 * SK_WARPS));
-        if (a.M <= 1) linear_skinny<T, 1><<<grid, SK_WARPS * 32, 0, st>>>(a);
-        else if (a.M <= 2) linear_skinny<T, 2><<<grid, SK_WARPS * 32, 0, st>>>(a);
-        else if (a.M <= 4) linear_skinny<T, 4><<<grid, SK_WARPS * 32, 0, st>>>(a);
-        else linear_skinny<T, 8><<<grid, SK_WARPS * 32, 0, st>>>(a);
+        dim3 grid2((a.N + 2 * SK_WARPS - 1) / (2 * SK_WARPS));  // two rows per warp measured faster than four at M = 8
+        if (a.M <= 1) linear_skinny<T, 1, 2><<<grid2, SK_WARPS * 32, 0, st>>>(a);
+        else if (a.M <= 2) linear_skinny<T, 2, 2><<<grid2, SK_WARPS * 32, 0, st>>>(a);
+        else if (a.M <= 4) linear_skinny<T, 4, 2><<<grid2, SK_WARPS * 32, 0, st>>>(a);
+        else linear_skinny<T, 8, 2><<<grid2, SK_WARPS * 32, 0, st>>>(a);
     } else if constexpr (sizeof(T) == 2) {
         dim3 grid((a.N + MM_BN - 1) / MM_BN, (a.M + MM_BM - 1) / MM_BM);
         linear_tiled_mma<<<grid, MM_THREADS, 0, st>>>(a);

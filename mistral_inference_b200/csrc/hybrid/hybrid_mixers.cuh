@@ -97,15 +97,18 @@ struct AttnArgs {
     void* out;              // [T, H*e]
     int T, B, W, H, G, d, e;
     float scale;
+    int splits;             // CTAs per (token, head) along the keys; > 1: partial (max, sum, acc) go to `scratch`
+    float* scratch;         // [T*H, splits, 2 + e] fp32
 };
 
 constexpr int AT_WARPS = 4, AT_CHUNK = 128, AT_MAXR = 8;  // e <= 32 * AT_MAXR
 
-// One CTA per (token, head); its warps take alternate chunks of AT_CHUNK keys (scores: lanes over keys; values: lanes
-// over the value columns) with a running (max, sum); the warps' partial results are merged through shared memory.
+// `splits` CTAs per (token, head); their warps take alternate chunks of AT_CHUNK keys (scores: lanes over keys, a whole key row
+// per lane; values: every lane owns ceil(e / 32) adjacent value columns) with a running (max, sum); the warps' partial results
+// are merged through shared memory, the CTAs' (decode: few queries, long contexts) by attn_merge_kernel.
 template <typename T>
 __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(AttnArgs a) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     const int t = blockIdx.x / a.H, h = blockIdx.x % a.H, g = h / (a.H / a.G);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* qs = sm;                                  // [d]
@@ -126,7 +129,8 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(AttnArgs a) {
     float m = -INFINITY, l = 0.f, acc[AT_MAXR];
 #pragma unroll
     for (int r = 0; r < AT_MAXR; ++r) acc[r] = 0.f;
-    for (int c0 = warp * AT_CHUNK; c0 < n; c0 += AT_WARPS * AT_CHUNK) {
+    const int cpl = (a.e + 31) / 32;  // value columns per lane: lane * cpl .. + cpl - 1
+    for (int c0 = (blockIdx.y * AT_WARPS + warp) * AT_CHUNK; c0 < n; c0 += a.splits * AT_WARPS * AT_CHUNK) {
         const int cn = min(AT_CHUNK, n - c0);
         float cmax = -INFINITY;
         for (int jj = lane; jj < cn; jj += 32) {
@@ -138,7 +142,10 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(AttnArgs a) {
                     float kv[V];
                     Vec<T>::load(kr + i, kv);
 #pragma unroll
-                    for (int u = 0; u < V; ++u) s = fmaf(qs[i + u], kv[u], s);
+                    for (int u = 0; u < V; u += 4) {  // q from shared memory four at a time (qs is 16-byte aligned, i % 4 == 0)
+                        const float4 q4 = *reinterpret_cast<const float4*>(qs + i + u);
+                        s = fmaf(q4.x, kv[u], s); s = fmaf(q4.y, kv[u + 1], s); s = fmaf(q4.z, kv[u + 2], s); s = fmaf(q4.w, kv[u + 3], s);
+                    }
                 }
             } else {
                 for (int i = 0; i < a.d; ++i) s = fmaf(qs[i], to_f(kr[i]), s);
@@ -158,13 +165,27 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(AttnArgs a) {
         m = m_new;
         __syncwarp();
 #pragma unroll
-        for (int r = 0; r < AT_MAXR; ++r) {
-            const int col = lane + 32 * r;
-            if (col < a.e) {
-                float o = acc[r] * corr;
-                const T* vp = Vp + col;
-                for (int jj = 0; jj < cn; ++jj) o = fmaf(sc[jj], to_f(vp[(size_t)((c0 + jj) % a.W) * vs]), o);
-                acc[r] = o;
+        for (int r = 0; r < AT_MAXR; ++r) acc[r] *= corr;
+        {
+            const T* vp = Vp + lane * cpl;
+            int jj = 0;
+            for (; jj + 4 <= cn; jj += 4) {
+                const T* r0 = vp + (size_t)((c0 + jj) % a.W) * vs;
+                const T* r1 = vp + (size_t)((c0 + jj + 1) % a.W) * vs;
+                const T* r2 = vp + (size_t)((c0 + jj + 2) % a.W) * vs;
+                const T* r3 = vp + (size_t)((c0 + jj + 3) % a.W) * vs;
+                const float w0 = sc[jj], w1 = sc[jj + 1], w2 = sc[jj + 2], w3 = sc[jj + 3];
+#pragma unroll
+                for (int r = 0; r < AT_MAXR; ++r)
+                    if (r < cpl && lane * cpl + r < a.e)
+                        acc[r] += w0 * to_f(r0[r]) + w1 * to_f(r1[r]) + w2 * to_f(r2[r]) + w3 * to_f(r3[r]);
+            }
+            for (; jj < cn; ++jj) {
+                const T* r0 = vp + (size_t)((c0 + jj) % a.W) * vs;
+                const float w0 = sc[jj];
+#pragma unroll
+                for (int r = 0; r < AT_MAXR; ++r)
+                    if (r < cpl && lane * cpl + r < a.e) acc[r] = fmaf(w0, to_f(r0[r]), acc[r]);
             }
         }
         __syncwarp();
@@ -189,12 +210,39 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(AttnArgs a) {
 #pragma unroll
             for (int r = 0; r < AT_MAXR; ++r) o[r] = fmaf(p[2 + r * 32 + lane], f, o[r]);
         }
-        T* out = static_cast<T*>(a.out) + ((size_t)t * a.H + h) * a.e;
+        if (a.splits > 1) {
+            float* part = a.scratch + ((size_t)blockIdx.x * a.splits + blockIdx.y) * (2 + a.e);
+            if (lane == 0) { part[0] = M; part[1] = L; }
 #pragma unroll
-        for (int r = 0; r < AT_MAXR; ++r) {
-            const int col = lane + 32 * r;
-            if (col < a.e) out[col] = from_f<T>(o[r] / L);
+            for (int r = 0; r < AT_MAXR; ++r)
+                if (r < cpl && lane * cpl + r < a.e) part[2 + lane * cpl + r] = o[r];
+        } else {
+            T* out = static_cast<T*>(a.out) + ((size_t)t * a.H + h) * a.e;
+#pragma unroll
+            for (int r = 0; r < AT_MAXR; ++r)
+                if (r < cpl && lane * cpl + r < a.e) out[lane * cpl + r] = from_f<T>(o[r] / L);
         }
+    }
+}
+
+// out[t, h, :] from the `splits` partial results of attn_bias_kernel
+template <typename T>
+__global__ void attn_merge_kernel(const float* __restrict__ scratch, T* __restrict__ out, int splits, int e) {
+    const float* part = scratch + (size_t)blockIdx.x * splits * (2 + e);
+    float M = -INFINITY;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, part[(size_t)s * (2 + e)]);
+    float L = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const float m = part[(size_t)s * (2 + e)];
+        if (m != -INFINITY) L += part[(size_t)s * (2 + e) + 1] * expf(m - M);
+    }
+    for (int c = threadIdx.x; c < e; c += blockDim.x) {
+        float o = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float m = part[(size_t)s * (2 + e)];
+            if (m != -INFINITY) o = fmaf(part[(size_t)s * (2 + e) + 2 + c], expf(m - M), o);
+        }
+        out[(size_t)blockIdx.x * e + c] = from_f<T>(o / L);
     }
 }
 

@@ -8,6 +8,7 @@ On disk: config.json + model.safetensors with tensors `embed`, `l<i>.norm1|norm2
 fp32 arithmetic.  All compute runs in libmb200_hybrid.so (include/mistral_b200_hybrid.h); CUDA only, no fallback.
 """
 import json
+import os
 from pathlib import Path
 from typing import Any, Dict, List, Optional, Tuple, Union
 
@@ -16,7 +17,7 @@ from torch import nn
 
 from . import _abi, _abi_hybrid as _h
 from .args import LayeredArgs
-from .cache import BufferCache
+from .cache import BufferCache, CacheInputMetadata
 from .transformer_layers import MIXERS, BiasedAttention, ClampedGLU, LayeredBlock, LightningMixer
 
 
@@ -73,16 +74,22 @@ class LayeredTransformer(nn.Module):
         assert sum(seqlens) == num_toks, (sum(seqlens), num_toks)
         if cache is None:
             cache = self.make_cache(len(seqlens), max(seqlens))
-        md = cache.get_input_metadata(seqlens)
+        self._check_room(cache, seqlens)
+        x = self._run_layers(input_ids, cache.get_input_metadata(seqlens), cache)
+        cache.update_seqlens(seqlens)
+        return x
+
+    def _check_room(self, cache: BufferCache, seqlens: List[int]) -> None:
         past = cache._kv_seqlens_host or [0] * len(seqlens)
         assert max(p + s for p, s in zip(past, seqlens)) <= cache.max_seq_len, "sequence longer than the cache"
+
+    def _run_layers(self, input_ids: torch.Tensor, md: List[CacheInputMetadata], cache: BufferCache) -> torch.Tensor:
         x = _h.embed_scale(input_ids, self.embed, self.args.embedding_scale)
         ctx: Dict[str, torch.Tensor] = {}
         for i, blk in enumerate(self.layers):
             blk(x, cache.get_view(i, md[i]), ctx)
             if self._tap is not None:
                 self._tap(i, x)
-        cache.update_seqlens(seqlens)
         return x
 
     _tap = None  # debugging hook: called with (layer, residual stream) after every layer
@@ -91,12 +98,58 @@ class LayeredTransformer(nn.Module):
         """Final norm + head, fp32 [rows, vocab]."""
         return _h.linear(_h.rmsnorm(x32, self.final_norm, self.args.norm_eps), self.head, epi=_h.EPI_F32)
 
+    def _graph_decode_ok(self, seqlens: List[int], cache: Optional[BufferCache]) -> bool:
+        if cache is None or self._tap is not None or os.environ.get("MB200_DECODE_GRAPH", "1") == "0":
+            return False
+        host = cache._kv_seqlens_host
+        return host is not None and len(host) == len(seqlens) and min(host) > 0 and all(s == 1 for s in seqlens)
+
+    @torch.inference_mode()
+    def decode_static(self, tokens: torch.Tensor, cache: BufferCache) -> torch.Tensor:
+        """One decode step for every live sequence of `cache`, replayed from a CUDA graph (the launch-bound inner loop of
+        generation; same scheme as `Transformer.decode_static` for batches).  The step's metadata block is built on the host and
+        copied into a static device buffer before the replay; the kernels' grids depend on the batch size only.  Returns the
+        STATIC fp32 logits [B, vocab] (overwritten by the next step).  The first call per (cache, batch) runs eagerly, the second
+        captures; `BufferCache.retire` drops the graphs of the old batch."""
+        self._check_runnable()
+        B = tokens.shape[0]
+        seqlens = [1] * B
+        self._check_room(cache, seqlens)
+        st = cache.__dict__.setdefault("_mb200_decode_states", {}).setdefault((id(self), "layered", B), {})
+        host, layout = cache.build_metadata_host(seqlens)
+        if "meta" not in st:
+            st.update({"meta": torch.zeros(len(host), dtype=torch.int32, device=self.device), "graph": None, "warmed": False, "logits": None,
+                       "tokens": torch.zeros(B, dtype=torch.long, device=self.device)})
+        st["meta"].copy_(torch.from_numpy(host))      # pageable source: staged by the runtime before the call returns
+        st["tokens"].copy_(tokens, non_blocking=True)
+        md = cache.metadata_from_block(st["meta"], layout, seqlens)
+
+        def run() -> None:
+            st["logits"] = self.logits_of(self._run_layers(st["tokens"], md, cache))
+
+        if st["graph"] is None and not st["warmed"]:
+            run()
+            st["warmed"] = True
+        elif st["graph"] is None:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                run()
+            st["graph"] = g
+            g.replay()
+        else:
+            st["graph"].replay()
+        cache.update_seqlens(seqlens)
+        return st["logits"]
+
     @torch.inference_mode()
     def forward(self, input_ids: torch.Tensor, seqlens: List[int], cache: Optional[BufferCache] = None,
                 rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """fp32 logits [T, vocab] of a ragged batch (or of the flattened token places `rows` only)."""
-        x = self.hidden(input_ids, seqlens, cache)
         self.last_argmax = None
+        if self._graph_decode_ok(seqlens, cache):
+            out = self.decode_static(input_ids, cache)
+            return out.clone() if rows is None else out.index_select(0, rows)
+        x = self.hidden(input_ids, seqlens, cache)
         return self.logits_of(x if rows is None else x.index_select(0, rows))
 
     # ------------------------------------------------------------------ generate() support
@@ -105,7 +158,11 @@ class LayeredTransformer(nn.Module):
 
     @torch.inference_mode()
     def next_token_logits(self, tokens: torch.Tensor, cache: BufferCache) -> torch.Tensor:
-        return self.forward(tokens.reshape(-1), [1] * tokens.numel(), cache)
+        """fp32 logits [B, vocab] of one decode step; on the graph path the step's static buffer (valid until the next step)."""
+        tokens = tokens.reshape(-1)
+        if self._graph_decode_ok([1] * tokens.numel(), cache):
+            return self.decode_static(tokens, cache)
+        return self.forward(tokens, [1] * tokens.numel(), cache)
 
     @torch.inference_mode()
     def forward_logprobs(self, input_ids: torch.Tensor, seqlens: List[int], cache: Optional[BufferCache],

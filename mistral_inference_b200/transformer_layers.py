@@ -195,6 +195,9 @@ from .args import BiasedAttentionArgs, ClampedGluArgs, LightningArgs  # noqa: E4
 from .cache import LayerCacheSpec  # noqa: E402
 
 
+FLASH_MIN_QUERIES = 16  # prompts (portions) at least this long take the tensor-core attention kernel in bf16
+
+
 def distance_buckets(rows: int, far: float) -> List[int]:
     """bucket(n) for n = 0 .. n_sat, where n_sat is the first distance in the last bucket: one row per distance below rows/2,
     then (rows - rows/2) logarithmic steps up to `far`.  Evaluated in double precision on the host, once per layer."""
@@ -255,7 +258,9 @@ class BiasedAttention(nn.Module):
                      a.heads, a.kv_heads, a.dim, a.vdim, self.eps, a.temp_coef, a.temp_every)
         out = torch.empty(T, a.heads * a.vdim, dtype=hn.dtype, device=hn.device)
         _h.attn_bias(q, view.cache_k, view.cache_v, self.bias_table(), md.positions, md.q_start, md.slots, out, len(md.seqlens), md.window,
-                     a.heads, a.kv_heads, a.dim, a.vdim, a.scale)
+                     a.heads, a.kv_heads, a.dim, a.vdim, a.scale,
+                     n_tiles=sum((n + 63) // 64 for n in md.seqlens) if md.max_seqlen >= FLASH_MIN_QUERIES else 0,
+                     splits=_h.attn_splits(T, a.heads, md.window))
         _h.linear(out, self.wo, epi=_h.EPI_RESIDUAL, residual=x32)
 
 
@@ -280,7 +285,7 @@ class LightningMixer(nn.Module):
         T = hn.shape[0]
         qkvg = _h.linear(hn, self.wqkvg, n_act=2 * self.nqk + self.nv)
         o32 = torch.empty(T, self.nv, dtype=torch.float32, device=hn.device)
-        _h.lightning_scan(qkvg, view.state, self.decay.float(), md.q_start, md.seqpos, md.slots, o32, len(md.seqlens), a.heads, a.dim, a.vdim)
+        _h.lightning_scan(qkvg, view.state, self.decay, md.q_start, md.seqpos, md.slots, o32, len(md.seqlens), a.heads, a.dim, a.vdim)
         y = _h.gated_headnorm(o32, self.norm, qkvg, qkvg.shape[1], 2 * self.nqk + self.nv, self.eps)
         _h.linear(y, self.wo, epi=_h.EPI_RESIDUAL, residual=x32)
 
@@ -306,7 +311,7 @@ MIXERS = {"attention": BiasedAttention, "lightning": LightningMixer}
 class LayeredBlock(nn.Module):
     """x <- x + mixer(norm1(x)); x <- x + ff(norm2(x)) when the layer has a feed-forward.  `x32` is updated in place."""
 
-    def __init__(self, width: int, eps: float, mixer: nn.Module, mlp: Optional[ClampedGLU], dtype_probe: str = "norm1"):
+    def __init__(self, width: int, eps: float, mixer: nn.Module, mlp: Optional[ClampedGLU]):
         super().__init__()
         self.eps = eps
         self.norm1 = nn.Parameter(torch.empty(width), requires_grad=False)
