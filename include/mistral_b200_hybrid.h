@@ -34,6 +34,10 @@ int mbh_rmsnorm(const void* x32, const void* w, void* y, int64_t T, int64_t D, f
 int mbh_linear(const void* x, const void* w, const void* bias, void* out, void* out32, int64_t M, int64_t N, int64_t K, int epi, int64_t n_act,
                float limit, float alpha, int dt, void* stream);
 
+/* The epilogues of mbh_linear alone, applied to y[M, N] (storage type, N even) that another GEMM produced. */
+int mbh_linear_epilogue(const void* y, const void* bias, void* out, void* out32, int64_t M, int64_t N, int epi, int64_t n_act, float limit, float alpha,
+                        int dt, void* stream);
+
 /* Splits qkv[T, H*d + G*d + G*e]; RMS-norms every q and k head over d with the shared weights qnorm / knorm [d] (null: no
  * norm); multiplies q at position p by 1 + temp_coef * ln(floor((p + 1) / temp_every) + 1) (temp_every = 0: no temperature);
  * value mixing: vmix_mode 0 none, 1 copy v to v_first[T, G*e], 2 v <- (1 - *vmix) v + *vmix v_first; then scatters k and v to

@@ -4,12 +4,13 @@ Same rules as `_abi`: the only place Python touches this library, and no fallbac
 in-tree by `build.build_hybrid()` (a fresh checkout has no binaries), a failing call raises.
 """
 import ctypes
+import os
 from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
 from typing import Optional
 
 import torch
 
-from . import build
+from . import _abi, build
 from ._abi import Mb200Error
 
 ABI_VERSION = 1
@@ -24,6 +25,7 @@ _SIGNATURES = {
     "mbh_embed_scale": (c_int, [P, P, F, P, I, I, c_int, P]),
     "mbh_rmsnorm": (c_int, [P, P, P, I, I, F, c_int, P]),
     "mbh_linear": (c_int, [P, P, P, P, P, I, I, I, c_int, I, F, F, c_int, P]),
+    "mbh_linear_epilogue": (c_int, [P, P, P, P, I, I, c_int, I, F, F, c_int, P]),
     "mbh_attn_prep": (c_int, [P, P, P, P, P, P, P, P, P, P, c_int, I, I, I, I, I, F, F, I, c_int, P]),
     "mbh_attn_bias": (c_int, [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, c_int, P]),
     "mbh_lightning_scan": (c_int, [P, P, P, P, P, P, P, I, I, I, I, c_int, P]),
@@ -84,6 +86,23 @@ def rmsnorm(x32: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     return y
 
 
+_ws: dict = {}
+
+
+def _workspace(device: torch.device) -> "_abi.Workspace":
+    if device not in _ws:
+        _ws[device] = _abi.Workspace(_abi.workspace_bytes(1, 64, 1, 1, 128, 64, 0, 1), device)
+    return _ws[device]
+
+
+def _prompt_gemm_ok(x: torch.Tensor, M: int, N: int, K: int) -> bool:
+    """Large bf16 Linears of prompts go to the main library's persistent tcgen05 GEMM when it is built and the shape fits its
+    tiles (K % 64 == 0, N % 128 == 0, at least one 128-row tile); everything else runs on this library's own kernels.  A checkout
+    that has only libmb200_hybrid.so never builds the main library for this."""
+    return (x.dtype == torch.bfloat16 and M >= 128 and K % 64 == 0 and N % 128 == 0 and os.environ.get("MB200_HYBRID_GEMM", "1") != "0"
+            and _abi.library_path().exists())
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, *, epi: int = EPI_STORE, n_act: int = 0,
            residual: Optional[torch.Tensor] = None, limit: float = 0.0, alpha: float = 0.0) -> torch.Tensor:
     """x [M, K] @ w [N, K]^T with the epilogues of include/mistral_b200_hybrid.h.  EPI_RESIDUAL adds into `residual` (fp32, in
@@ -99,6 +118,13 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
         out32 = torch.empty(M, N, dtype=torch.float32, device=x.device)
     else:
         out = torch.empty(M, N // 2 if epi == EPI_GLU else N, dtype=x.dtype, device=x.device)
+    if _prompt_gemm_ok(x, M, N, K):
+        # the framework's tcgen05 GEMM (bf16 out), then this library's epilogue over its result
+        y = torch.empty(M, N, dtype=x.dtype, device=x.device)
+        _abi.linear_residual(x, w, None, y, _workspace(x.device))
+        _check(lib().mbh_linear_epilogue(_ptr(y), _ptr(bias), _ptr(out), _ptr(out32), M, N, epi, n_act, limit, alpha, dt_of(x.dtype), _stream()),
+               "mbh_linear_epilogue")
+        return out if out is not None else out32
     _check(lib().mbh_linear(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _ptr(out32), M, N, K, epi, n_act, limit, alpha, dt_of(x.dtype), _stream()),
            "mbh_linear")
     return out if out is not None else out32

@@ -29,7 +29,7 @@ static int bad(const char* what) {
 
 template <typename T>
 static cudaError_t launch_lightning(const LightningArgs& a, cudaStream_t st) {
-    const int threads = a.e >= 128 ? 128 : ((a.e + 31) / 32) * 32;
+    const int threads = LS_THREADS;
     dim3 grid(a.B * a.H, (a.e + threads - 1) / threads);
     if (a.d <= 32) lightning_scan_kernel<T, 32><<<grid, threads, 0, st>>>(a);
     else if (a.d <= 64) lightning_scan_kernel<T, 64><<<grid, threads, 0, st>>>(a);
@@ -43,6 +43,10 @@ template <typename T> static void run_embed(const void* tokens, const void* tabl
 }
 template <typename T> static void run_rmsnorm(const void* x32, const void* w, void* y, int64_t T_, int64_t D, float eps, cudaStream_t st) {
     rmsnorm_f32_kernel<T><<<(unsigned)T_, D >= 1024 ? 256 : 128, 0, st>>>((const float*)x32, (const T*)w, (T*)y, (int)D, eps);
+}
+template <typename T> static void run_epilogue(const LinearArgs& a, const void* y, cudaStream_t st) {
+    const size_t pairs = (size_t)a.M * (a.N >> 1);
+    linear_epilogue_kernel<T><<<(unsigned)((pairs + 255) / 256), 256, 0, st>>>(a, (const T*)y);
 }
 template <typename T> static void run_prep(const AttnPrepArgs& a, int64_t T_, cudaStream_t st) { attn_prep_kernel<T><<<(unsigned)T_, 128, 0, st>>>(a); }
 template <typename T> static void run_attn(const AttnArgs& a, size_t smem, cudaStream_t st) {
@@ -83,6 +87,17 @@ int mbh_linear(const void* x, const void* w, const void* bias, void* out, void* 
     cudaError_t e = cudaSuccess;
     DISPATCH(dt, e = launch_linear<ST>(a, (cudaStream_t)stream));
     return e ? fail(e, "mbh_linear") : 0;
+}
+
+int mbh_linear_epilogue(const void* y, const void* bias, void* out, void* out32, int64_t M, int64_t N, int epi, int64_t n_act, float limit, float alpha,
+                        int dt, void* stream) {
+    if (epi < 0 || epi > 3 || (N & 1)) return bad("mbh_linear_epilogue: unknown epilogue or odd N");
+    if (M == 0) return 0;
+    LinearArgs a{nullptr, nullptr, bias, out, (float*)out32, (int)M, (int)N, 0, epi, (int)n_act, limit, alpha};
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, run_epilogue<ST>(a, y, st));
+    cudaError_t e = cudaGetLastError();
+    return e ? fail(e, "mbh_linear_epilogue") : 0;
 }
 
 int mbh_attn_prep(const void* qkv, const void* qnorm, const void* knorm, const void* positions, const void* cache_rows, void* q_out, void* cache_k,

@@ -292,6 +292,16 @@ __global__ void __launch_bounds__(SKM_WARPS * 32) linear_skinny_mma(LinearArgs a
     }
 }
 
+// The epilogues alone, over a Linear output y[M, N] (storage type, N even) that another GEMM produced
+template <typename T>
+__global__ void linear_epilogue_kernel(LinearArgs a, const T* __restrict__ y) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t pairs = (size_t)a.M * (a.N >> 1);
+    if (idx >= pairs) return;
+    const int m = (int)(idx / (a.N >> 1)), n = (int)(idx % (a.N >> 1)) * 2;
+    epilogue_pair<T>(a, m, n, to_f(y[(size_t)m * a.N + n]), to_f(y[(size_t)m * a.N + n + 1]), true);
+}
+
 template <typename T>
 inline cudaError_t launch_linear(const LinearArgs& a, cudaStream_t st) {
     if (a.M <= 0 || a.N <= 0) return cudaSuccess;

@@ -258,45 +258,66 @@ struct LightningArgs {
     int B, H, d, e;
 };
 
-constexpr int LS_TB = 16;
+constexpr int LS_TB = 16, LS_THREADS = 128;
 
-// One CTA per (sequence, head, block of value columns); thread c owns column c of the state: DMAX registers.  Keys and queries
-// of LS_TB tokens at a time are staged through shared memory.  Sequential in t, exact in fp32.
+// One CTA of LS_THREADS threads per (sequence, head, block of LS_THREADS value columns); thread c owns column c of the state:
+// DMAX registers.  Keys and queries of LS_TB tokens at a time go through shared memory; the next LS_TB tokens are fetched into
+// registers while the current ones are consumed, so the scan does not wait for global memory.  Sequential in t, exact in fp32.
 template <typename T, int DMAX>
-__global__ void lightning_scan_kernel(LightningArgs a) {
-    __shared__ float ks[LS_TB][DMAX], qs[LS_TB][DMAX];
+__global__ void __launch_bounds__(LS_THREADS) lightning_scan_kernel(LightningArgs a) {
+    constexpr int R = 2 * LS_TB * DMAX / LS_THREADS;  // staged values per thread and tile
+    __shared__ __align__(16) float ks[LS_TB][DMAX], qs[LS_TB][DMAX];
     const int b = blockIdx.x / a.H, h = blockIdx.x % a.H;
-    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    const int c = blockIdx.y * LS_THREADS + threadIdx.x;
     const bool live = c < a.e;
     const int t0 = a.q_start[b], t1 = a.q_start[b + 1];
     const int stride = 2 * a.H * a.d + 2 * a.H * a.e;
     const T* X = static_cast<const T*>(a.qkvg);
     float* st = a.state + (((size_t)a.slots[b] * a.H + h) * a.d) * a.e;
     const float dec = a.decay[h];
-    float S[DMAX];
+    float S[DMAX], pre[R];
     const bool fresh = a.seqpos[b] == 0;
 #pragma unroll
     for (int i = 0; i < DMAX; ++i) S[i] = (live && !fresh && i < a.d) ? st[(size_t)i * a.e + c] : 0.f;
+
+    auto fetch = [&](int tb) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int idx = threadIdx.x + r * LS_THREADS;
+            const int tt = idx / (2 * DMAX), rem = idx % (2 * DMAX), which = rem / DMAX, i = rem % DMAX;
+            const bool ok = tb + tt < t1 && i < a.d;
+            pre[r] = ok ? to_f(X[(size_t)(tb + tt) * stride + (which ? a.H * a.d : 0) + h * a.d + i]) : 0.f;
+        }
+    };
+    fetch(t0);
     for (int tb = t0; tb < t1; tb += LS_TB) {
         const int nt = min(LS_TB, t1 - tb);
         __syncthreads();
-        for (int idx = threadIdx.x; idx < nt * DMAX; idx += blockDim.x) {
-            const int tt = idx / DMAX, i = idx % DMAX;
-            const T* row = X + (size_t)(tb + tt) * stride;
-            qs[tt][i] = i < a.d ? to_f(row[h * a.d + i]) : 0.f;
-            ks[tt][i] = i < a.d ? to_f(row[a.H * a.d + h * a.d + i]) : 0.f;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int idx = threadIdx.x + r * LS_THREADS;
+            const int tt = idx / (2 * DMAX), rem = idx % (2 * DMAX), which = rem / DMAX, i = rem % DMAX;
+            (which ? ks : qs)[tt][i] = pre[r];
         }
         __syncthreads();
+        if (tb + LS_TB < t1) fetch(tb + LS_TB);
         if (live) {
+            const T* vcol = X + 2 * a.H * a.d + h * a.e + c;
+            float vn = to_f(vcol[(size_t)tb * stride]);
             for (int tt = 0; tt < nt; ++tt) {
-                const float v = to_f(X[(size_t)(tb + tt) * stride + 2 * a.H * a.d + h * a.e + c]);
-                float o = 0.f;
+                const float v = vn;
+                if (tt + 1 < nt) vn = to_f(vcol[(size_t)(tb + tt + 1) * stride]);  // in flight while this token is consumed
+                float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;  // four chains: the sum over i is not one dependent chain of DMAX FMAs
 #pragma unroll
-                for (int i = 0; i < DMAX; ++i) {
-                    S[i] = fmaf(dec, S[i], ks[tt][i] * v);
-                    o = fmaf(S[i], qs[tt][i], o);
+                for (int i = 0; i < DMAX; i += 4) {
+                    const float4 k4 = *reinterpret_cast<const float4*>(&ks[tt][i]);
+                    const float4 q4 = *reinterpret_cast<const float4*>(&qs[tt][i]);
+                    S[i] = fmaf(dec, S[i], k4.x * v);         o0 = fmaf(S[i], q4.x, o0);
+                    S[i + 1] = fmaf(dec, S[i + 1], k4.y * v); o1 = fmaf(S[i + 1], q4.y, o1);
+                    S[i + 2] = fmaf(dec, S[i + 2], k4.z * v); o2 = fmaf(S[i + 2], q4.z, o2);
+                    S[i + 3] = fmaf(dec, S[i + 3], k4.w * v); o3 = fmaf(S[i + 3], q4.w, o3);
                 }
-                a.o[(size_t)(tb + tt) * a.H * a.e + h * a.e + c] = o;
+                a.o[(size_t)(tb + tt) * a.H * a.e + h * a.e + c] = (o0 + o1) + (o2 + o3);
             }
         }
     }

@@ -49,7 +49,7 @@ def _close(got, ref, dtype, what=""):
 
 # ----------------------------------------------------------------------------- mechanisms alone
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("M,N,K", [(1, 10, 7), (3, 33, 40), (8, 64, 64), (5, 50, 296), (4, 37, 23), (9, 50, 24), (70, 130, 100), (200, 96, 328)])
+@pytest.mark.parametrize("M,N,K", [(1, 10, 7), (3, 33, 40), (8, 64, 64), (5, 50, 296), (4, 37, 23), (9, 50, 24), (70, 130, 100), (200, 96, 328), (256, 256, 128), (130, 384, 64)])
 def test_linear_epilogues(dtype, M, N, K):
     from mistral_inference_b200 import _abi_hybrid as h
 
