@@ -125,7 +125,7 @@ def kernel_table(s: dict, T: int, ctx: int, peaks: dict, dev) -> dict:
 
     x = torch.randn(T, W, device=dev).to(bf)
     w13 = torch.randn(2 * ff, W, device=dev).to(bf) * 0.02
-    rec("linear_tiled_mma gate/up+glu", _time(lambda: h.linear(x, w13, epi=h.EPI_GLU, limit=7.0, alpha=1.702), 3, 8, flush), flops=2.0 * T * 2 * ff * W)
+    rec("prompt linear gate/up+glu (tcgen05 GEMM + epilogue pass)", _time(lambda: h.linear(x, w13, epi=h.EPI_GLU, limit=7.0, alpha=1.702), 3, 8, flush), flops=2.0 * T * 2 * ff * W)
     for M in (1, 8):
         xs = x[:M].contiguous()
         rec(f"linear_skinny gate/up+glu M={M}", _time(lambda: h.linear(xs, w13, epi=h.EPI_GLU, limit=7.0, alpha=1.702), 3, 8, flush), bytes_=w13.numel() * 2.0)

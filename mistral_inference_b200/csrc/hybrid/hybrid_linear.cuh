@@ -9,9 +9,10 @@
 // In bf16 mode the Linear's own output is rounded to bf16 before the epilogue's arithmetic (the rounding point of a bf16
 // Linear); accumulation is fp32 in both modes.
 //
-// Two kernels: `linear_tiled` for prompts (64 x 64 output tile per CTA, K staged through shared memory; bf16 operands go
-// through mma.sync m16n8k16 tensor-core tiles, fp32 operands through FMA), and `linear_skinny` for M <= 8 rows
-// (decode: one warp per pair of weight rows, every weight byte read once, coalesced 16-byte loads).
+// Kernels: `linear_tiled_mma` (bf16) and `linear_tiled_fma` (fp32) for prompts, any shape; `linear_skinny` (M <= 8 rows, FMA,
+// one warp per pair of weight rows) and `linear_skinny_mma` (bf16, 3..8 rows, tensor cores) for decode: every weight byte is read
+// once with 16-byte loads; `linear_epilogue_kernel` applies the epilogues to the output of another GEMM (the main library's
+// tcgen05 GEMM takes the large aligned bf16 Linears of prompts, see _abi_hybrid.linear).
 #pragma once
 #include "hybrid_common.cuh"
 

@@ -11,7 +11,7 @@ from tests import fesenex_oracle as O
 from tests.fesenex_util import make_config
 
 
-@pytest.mark.parametrize("rows,far", [(32, 240.0), (8, 64.0), (16, 1000.0), (4, 3.0), (64, 33.0)])
+@pytest.mark.parametrize("rows,far", [(30, 200.0), (8, 64.0), (16, 1000.0), (4, 3.0), (64, 33.0)])
 def test_distance_buckets_match_the_oracle(rows, far):
     tab = distance_buckets(rows, far)
     assert tab[-1] == rows - 1 and all(b < rows - 1 for b in tab[:-1])

@@ -18,9 +18,9 @@ SHAPES = {
     # heads == kv_heads, one kv head, value size above key size, sizes that are no multiple of 8, lightning first, no feed-forward last
     "odd": dict(width=44, vocab=37, layers=[("lightning", dict(heads=3, dim=20, vdim=36)), ("attention", dict(heads=3, kv_heads=3, dim=12, vdim=20, _rel_rows=6, bias_max=9)),
                                             ("attention", dict(heads=4, kv_heads=1, dim=24, vdim=40, v_mix=True, _rel_rows=12, bias_max=100), None)]),
-    "wide": dict(width=96, vocab=80, layers=[("attention", dict(heads=8, kv_heads=2, dim=64, vdim=32, v_mix=True, _rel_rows=32, bias_max=240, q_temp={"coef": 0.7, "every": 16})),
+    "wide": dict(width=96, vocab=80, layers=[("attention", dict(heads=6, kv_heads=2, dim=64, vdim=32, v_mix=True, _rel_rows=24, bias_max=200, q_temp={"coef": 0.7, "every": 16})),
                                              ("lightning", dict(heads=2, dim=64, vdim=64)), ("lightning", dict(heads=1, dim=96, vdim=16), None),
-                                             ("attention", dict(heads=8, kv_heads=2, dim=64, vdim=32, v_mix=True, _rel_rows=32, bias_max=240))]),
+                                             ("attention", dict(heads=6, kv_heads=2, dim=64, vdim=32, v_mix=True, _rel_rows=24, bias_max=200))]),
 }
 
 
