@@ -66,3 +66,19 @@ def test_registry_picks_the_class_by_the_folder(tmp_path):
     assert registry.architecture_of(tmp_path / "b") == "transformer"
     with pytest.raises(ValueError):
         registry.architecture_of(tmp_path / "c")
+
+
+def test_hybrid_binding_matches_the_header():
+    """Every function the header declares is bound with as many arguments, and nothing else is bound."""
+    import re
+    from pathlib import Path
+
+    from mistral_inference_b200 import _abi_hybrid
+
+    text = (Path(__file__).resolve().parent.parent / "include" / "mistral_b200_hybrid.h").read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    decl = {m.group(1): m.group(2) for m in re.finditer(r"\b(mbh_\w+)\s*\(([^;]*?)\)\s*;", text, flags=re.S)}
+    assert set(decl) == set(_abi_hybrid._SIGNATURES)
+    for name, params in decl.items():
+        n = 0 if params.strip() == "void" else params.count(",") + 1
+        assert n == len(_abi_hybrid._SIGNATURES[name][1]), name

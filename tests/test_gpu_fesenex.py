@@ -300,3 +300,37 @@ def test_exact_attention_with_split_keys(dtype, splits):
     h.attn_bias(q, cache.cache_k[0], cache.cache_v[0], tab, md.positions, md.q_start, md.slots, out, len(lens), W, H, G, d, e, scale, splits=splits)
     err = (out.float().cpu() - ref).abs().max() / ref.abs().max()
     assert err < (1e-4 if dtype == torch.float32 else 0.02), err
+
+
+def test_trace_runner_replays_a_schedule(tmp_path):
+    """bin/trace_run on a small folder: a ragged batch that starts together, decodes, loses its shorter request, then a second
+    batch in the same rows; the files it writes hold the oracle's logits at the places asked for."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    import numpy as np
+
+    cfg = make_config(**SHAPES["mixed"])
+    w = make_weights(cfg, 5)
+    folder = write_folder(tmp_path / "model", cfg, w)
+    cfg = clean_config(cfg)
+    a, b, c = _tokens(cfg, 20, 31), _tokens(cfg, 9, 32), _tokens(cfg, 26, 33)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:18], "want": [0, 17]}, {"id": "b", "tokens": b[:8], "want": [7]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": a[18:19], "want": []}, {"id": "b", "tokens": b[8:9], "want": [0]}], "end": ["b"]},
+             {"step": 2, "entries": [{"id": "a", "tokens": a[19:20], "want": [0]}], "end": ["a"]},
+             {"step": 3, "entries": [{"id": "c", "tokens": c[:24], "want": [23]}], "end": []},
+             {"step": 4, "entries": [{"id": "c", "tokens": c[24:25], "want": [0]}], "end": []},
+             {"step": 5, "entries": [{"id": "c", "tokens": c[25:26], "want": [0]}], "end": ["c"]}]
+    out = tmp_path / "out"
+    exe = Path(__file__).resolve().parent.parent / "bin" / "trace_run"
+    r = subprocess.run([sys.executable, str(exe), "--model", str(folder), "--dtype", "float32", "--out", str(out), "--max-tokens", "64"],
+                       input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [ln for ln in r.stdout.split("\n") if ln.startswith("done")] == [f"done {i}" for i in range(6)]
+    ra, rb, rc = (O.forward(cfg, w, t) for t in (a, b, c))
+    want = {0: torch.stack([ra[0], ra[17], rb[7]]), 1: rb[8:9], 2: ra[19:20], 3: rc[23:24], 4: rc[24:25], 5: rc[25:26]}
+    for n, ref in want.items():
+        got = torch.from_numpy(np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(-1, cfg["vocab"]))
+        _close(got, ref, torch.float32, f"step {n}")
