@@ -267,6 +267,7 @@ __global__ void __launch_bounds__(SKM_WARPS * 32) linear_skinny_mma(LinearArgs a
     const bool xrow = gid < a.M;
     const bf16* xr = X + (size_t)(xrow ? gid : 0) * a.K;
     float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4  // four steps of loads in flight per warp: the kernel waits on global memory, not on the tensor pipe
     for (int kb = warp * 32; kb < a.K; kb += SKM_WARPS * 32) {
         const int k = kb + tig * 8;
         uint4 va = make_uint4(0, 0, 0, 0), vb = va, vx = va;
