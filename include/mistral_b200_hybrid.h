@@ -13,7 +13,7 @@
 extern "C" {
 #endif
 
-#define MBH_ABI_VERSION 1
+#define MBH_ABI_VERSION 2
 
 int mbh_abi_version(void);
 const char* mbh_last_error(void);
@@ -64,6 +64,56 @@ int mbh_lightning_scan(const void* qkvg, void* state, const void* decay, const v
 /* y[t, :] = rms_norm(o32[t, :N]; eps) * w * sigmoid(g[t * g_pitch + g_off + :N]). */
 int mbh_gated_headnorm(const void* o32, const void* w, const void* g, int64_t g_pitch, int64_t g_off, void* y, int64_t T, int64_t N, float eps,
                        int dt, void* stream);
+
+/* x32[t, :] += table[tokens[t], :] * scale (the embedding added again to the residual stream). */
+int mbh_embed_add(const void* tokens, const void* table, float scale, void* x32, int64_t T, int64_t D, int dt, void* stream);
+
+/* Layer norm of fp32 rows x32 [T, D]: (x - mean) / sqrt(var + eps) * w + b, var = mean of the squared deviations; b may be null.
+ * Exactly one of y (storage type [T, D]: y = norm) and acc32 (fp32 [T, D]: acc32 += norm, in fp32) is given. */
+int mbh_layernorm(const void* x32, const void* w, const void* b, void* y, void* acc32, int64_t T, int64_t D, float eps, int dt, void* stream);
+
+/* Linear with interleaved gate/up rows (as epilogue 2 of mbh_linear) and out[M, N/2] = silu(gate) * up * rowscale[m, c / rs_group];
+ * rowscale: fp32 [M, rs_pitch] or null (no scaling).  mbh_swiglu_epilogue applies the same to y[M, N] of another GEMM. */
+int mbh_linear_swiglu(const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K, const void* rowscale, int64_t rs_pitch,
+                      int64_t rs_group, int dt, void* stream);
+int mbh_swiglu_epilogue(const void* y, void* out, int64_t M, int64_t N, const void* rowscale, int64_t rs_pitch, int64_t rs_group, int dt,
+                        void* stream);
+
+/* Latent attention, input side.  y [T, pitch] = [query latent (q_rank) | key/value latent (kv_rank) | shared rotated key part
+ * (rot_dim) | ...].  cq [T, q_rank] = rms_norm(query latent) * qnorm; ring row cache_rows[t] (-1: not cached) of ring
+ * [rows, kv_rank + rot_dim] = [rms_norm(kv latent) * cnorm | rot(key part)].  rot: the pairs (2i, 2i+1), i < rot_dims / 2, turn by
+ * positions[t] * freq[i] (freq: float64 [rot_dims / 2]), cos and sin times mag; entries from rot_dims on pass unchanged. */
+int mbh_latent_prep(const void* y, const void* qnorm, const void* cnorm, const void* freq, const void* positions, const void* cache_rows, void* cq,
+                    void* ring, int64_t T, int64_t pitch, int64_t q_rank, int64_t kv_rank, int64_t rot_dim, int64_t rot_dims, float eps, float mag,
+                    int dt, void* stream);
+
+/* q [T, H, dn + rot_dim] -> qa [T, H, kv_rank + rot_dim] = [W_uk[h]^T q[:dn] | rot(q[dn:])], w_uk [H * dn, kv_rank]. */
+int mbh_latent_absorb(const void* q, const void* w_uk, const void* freq, const void* positions, void* qa, int64_t T, int64_t H, int64_t dn,
+                      int64_t rot_dim, int64_t rot_dims, int64_t kv_rank, float mag, int dt, void* stream);
+
+/* Causal softmax attention of qa over latent rows: score = qa . ring row * scale, value = the row's first kv_rank entries;
+ * o_lat [T, H, kv_rank].  Ring addressing, splits and scratch as mbh_attn_bias (exact fp32 kernel, one key/value head). */
+int mbh_attn_latent(const void* qa, const void* ring, const void* positions, const void* q_start, const void* slots, void* o_lat, int64_t T,
+                    int64_t B, int64_t W, int64_t H, int64_t kv_rank, int64_t rot_dim, float scale, int64_t splits, void* scratch, int dt,
+                    void* stream);
+
+/* out [T, H * dv] = (W_uv[h] o_lat[t, h]) * sigmoid(gate[t * g_pitch + g_off + h]); w_uv [H * dv, kv_rank]; gate null: no gate. */
+int mbh_latent_vup(const void* o_lat, const void* w_uv, const void* gate, int64_t g_pitch, int64_t g_off, void* out, int64_t T, int64_t H,
+                   int64_t dv, int64_t kv_rank, int dt, void* stream);
+
+/* Router of a mixture of experts, fp32: s = softmax(W_r h) over n outputs, choice = s + correction (null: none); the outputs form
+ * `groups` equal groups of neighbours and only those of the `keep` groups with the largest choice stay eligible; the `top` largest
+ * eligible choices are taken, weighted by s.  dense: fp32 [T, n] (0 where not chosen); idx int32 / wsel fp32 [T, top]. */
+int mbh_moe_route(const void* h, const void* w_router, const void* correction, void* dense, void* idx, void* wsel, int64_t T, int64_t width,
+                  int64_t n, int64_t groups, int64_t keep, int64_t top, int dt, void* stream);
+
+/* The chosen experts of few tokens: y32 [T, width] = sum_k wsel[t, k] * expert(idx[t, k])(h[t]); an index >= E is an identity
+ * expert (output = h[t]).  w13 [E * 2 * ff, width] (gate and up rows interleaved), w2 [width, E * ff]; act: scratch [T * top, ff]. */
+int mbh_moe_sparse(const void* h, const void* w13, const void* w2, const void* idx, const void* wsel, void* act, void* y32, int64_t T, int64_t width,
+                   int64_t ff, int64_t E, int64_t top, int dt, void* stream);
+
+/* y32[t, :] += (dense[t, first] + ... + dense[t, n - 1]) * h[t, :]. */
+int mbh_rows_axpy(void* y32, const void* h, const void* dense, int64_t T, int64_t n, int64_t first, int64_t D, int dt, void* stream);
 
 #ifdef __cplusplus
 }

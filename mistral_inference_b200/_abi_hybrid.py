@@ -13,7 +13,7 @@ import torch
 from . import _abi, build
 from ._abi import Mb200Error
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 EPI_STORE, EPI_RESIDUAL, EPI_GLU, EPI_F32 = 0, 1, 2, 3
 _DT = {torch.bfloat16: 0, torch.float32: 1}
 _lib: Optional[ctypes.CDLL] = None
@@ -30,6 +30,17 @@ _SIGNATURES = {
     "mbh_attn_bias": (c_int, [P, P, P, P, I, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P, c_int, P]),
     "mbh_lightning_scan": (c_int, [P, P, P, P, P, P, P, I, I, I, I, c_int, P]),
     "mbh_gated_headnorm": (c_int, [P, P, P, I, I, P, I, I, F, c_int, P]),
+    "mbh_embed_add": (c_int, [P, P, F, P, I, I, c_int, P]),
+    "mbh_layernorm": (c_int, [P, P, P, P, P, I, I, F, c_int, P]),
+    "mbh_linear_swiglu": (c_int, [P, P, P, I, I, I, P, I, I, c_int, P]),
+    "mbh_swiglu_epilogue": (c_int, [P, P, I, I, P, I, I, c_int, P]),
+    "mbh_latent_prep": (c_int, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, c_int, P]),
+    "mbh_latent_absorb": (c_int, [P, P, P, P, P, I, I, I, I, I, I, F, c_int, P]),
+    "mbh_attn_latent": (c_int, [P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, c_int, P]),
+    "mbh_latent_vup": (c_int, [P, P, P, I, I, P, I, I, I, I, c_int, P]),
+    "mbh_moe_route": (c_int, [P, P, P, P, P, P, I, I, I, I, I, I, c_int, P]),
+    "mbh_moe_sparse": (c_int, [P, P, P, P, P, P, P, I, I, I, I, I, c_int, P]),
+    "mbh_rows_axpy": (c_int, [P, P, P, I, I, I, I, c_int, P]),
 }
 
 
@@ -163,3 +174,110 @@ def gated_headnorm(o32, w, g, g_pitch: int, g_off: int, eps: float) -> torch.Ten
     y = torch.empty(T, N, dtype=w.dtype, device=o32.device)
     _check(lib().mbh_gated_headnorm(_ptr(o32), _ptr(w), _ptr(g), g_pitch, g_off, _ptr(y), T, N, eps, dt_of(w.dtype), _stream()), "mbh_gated_headnorm")
     return y
+
+
+# ------------------------------------------------------------------------------------------------ layer norm, re-added embedding
+def embed_add(tokens: torch.Tensor, table: torch.Tensor, scale: float, x32: torch.Tensor) -> torch.Tensor:
+    """x32 += table[tokens] * scale."""
+    T, D = tokens.shape[0], table.shape[1]
+    assert tokens.dtype == torch.long and x32.dtype == torch.float32 and x32.shape == (T, D)
+    _check(lib().mbh_embed_add(_ptr(tokens), _ptr(table), scale, _ptr(x32), T, D, dt_of(table.dtype), _stream()), "mbh_embed_add")
+    return x32
+
+
+def layernorm(x32: torch.Tensor, w: torch.Tensor, b: Optional[torch.Tensor], eps: float, add_to: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Layer norm of fp32 rows.  Returns the normed rows in the weights' dtype, or, with `add_to` (fp32), adds them to it in fp32."""
+    T, D = x32.shape
+    assert x32.dtype == torch.float32
+    if add_to is not None:
+        assert add_to.dtype == torch.float32 and add_to.shape == x32.shape
+        y = None
+    else:
+        y = torch.empty(T, D, dtype=w.dtype, device=x32.device)
+    _check(lib().mbh_layernorm(_ptr(x32), _ptr(w), _ptr(b), _ptr(y), _ptr(add_to), T, D, eps, dt_of(w.dtype), _stream()), "mbh_layernorm")
+    return y if add_to is None else add_to
+
+
+# ------------------------------------------------------------------------------------------------ gated feed-forward, experts
+def linear_swiglu(x: torch.Tensor, w: torch.Tensor, rowscale: Optional[torch.Tensor] = None, group: int = 0) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) with gate/up rows interleaved in w [2F, K]; column c is multiplied by rowscale[m, c // group]."""
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and x.dtype == w.dtype and N % 2 == 0
+    pitch = 0
+    if rowscale is not None:
+        assert rowscale.dtype == torch.float32 and rowscale.shape[0] == M and group > 0 and (N // 2 + group - 1) // group <= rowscale.shape[1]
+        pitch = rowscale.shape[1]
+    out = torch.empty(M, N // 2, dtype=x.dtype, device=x.device)
+    if _prompt_gemm_ok(x, M, N, K):
+        y = torch.empty(M, N, dtype=x.dtype, device=x.device)
+        _abi.linear_residual(x, w, None, y, _workspace(x.device))
+        _check(lib().mbh_swiglu_epilogue(_ptr(y), _ptr(out), M, N, _ptr(rowscale), pitch, group, dt_of(x.dtype), _stream()), "mbh_swiglu_epilogue")
+        return out
+    _check(lib().mbh_linear_swiglu(_ptr(x), _ptr(w), _ptr(out), M, N, K, _ptr(rowscale), pitch, group, dt_of(x.dtype), _stream()), "mbh_linear_swiglu")
+    return out
+
+
+def moe_route(h: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], groups: int, keep: int, top: int):
+    """(dense fp32 [T, n], idx int32 [T, top], wsel fp32 [T, top]) of the fp32 router."""
+    T, D = h.shape
+    n = w_router.shape[0]
+    dense = torch.empty(T, n, dtype=torch.float32, device=h.device)
+    idx = torch.empty(T, top, dtype=torch.int32, device=h.device)
+    wsel = torch.empty(T, top, dtype=torch.float32, device=h.device)
+    _check(lib().mbh_moe_route(_ptr(h), _ptr(w_router), _ptr(correction), _ptr(dense), _ptr(idx), _ptr(wsel), T, D, n, groups, keep, top,
+                               dt_of(h.dtype), _stream()), "mbh_moe_route")
+    return dense, idx, wsel
+
+
+def moe_sparse(h: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, idx: torch.Tensor, wsel: torch.Tensor, E: int, ff: int) -> torch.Tensor:
+    """fp32 [T, width]: the weighted sum of each token's chosen experts (indices >= E: identity), streaming only their weights."""
+    T, D = h.shape
+    top = idx.shape[1]
+    act = torch.empty(T * top, ff, dtype=h.dtype, device=h.device)
+    y32 = torch.empty(T, D, dtype=torch.float32, device=h.device)
+    _check(lib().mbh_moe_sparse(_ptr(h), _ptr(w13), _ptr(w2), _ptr(idx), _ptr(wsel), _ptr(act), _ptr(y32), T, D, ff, E, top, dt_of(h.dtype), _stream()),
+           "mbh_moe_sparse")
+    return y32
+
+
+def rows_axpy(y32: torch.Tensor, h: torch.Tensor, dense: torch.Tensor, first: int) -> None:
+    """y32[t] += (dense[t, first:].sum()) * h[t]."""
+    T, D = h.shape
+    _check(lib().mbh_rows_axpy(_ptr(y32), _ptr(h), _ptr(dense), T, dense.shape[1], first, D, dt_of(h.dtype), _stream()), "mbh_rows_axpy")
+
+
+# ------------------------------------------------------------------------------------------------ latent attention
+def latent_prep(y, qnorm, cnorm, freq, positions, cache_rows, ring, q_rank: int, kv_rank: int, rot_dim: int, rot_dims: int, eps: float,
+                mag: float) -> torch.Tensor:
+    assert freq.dtype == torch.float64 and freq.numel() == rot_dims // 2
+    T = y.shape[0]
+    cq = torch.empty(T, q_rank, dtype=y.dtype, device=y.device)
+    _check(lib().mbh_latent_prep(_ptr(y), _ptr(qnorm), _ptr(cnorm), _ptr(freq), _ptr(positions), _ptr(cache_rows), _ptr(cq), _ptr(ring), T,
+                                 y.shape[1], q_rank, kv_rank, rot_dim, rot_dims, eps, mag, dt_of(y.dtype), _stream()), "mbh_latent_prep")
+    return cq
+
+
+def latent_absorb(q, w_uk, freq, positions, H: int, dn: int, rot_dim: int, rot_dims: int, kv_rank: int, mag: float) -> torch.Tensor:
+    T = q.shape[0]
+    qa = torch.empty(T, H * (kv_rank + rot_dim), dtype=q.dtype, device=q.device)
+    _check(lib().mbh_latent_absorb(_ptr(q), _ptr(w_uk), _ptr(freq), _ptr(positions), _ptr(qa), T, H, dn, rot_dim, rot_dims, kv_rank, mag,
+                                   dt_of(q.dtype), _stream()), "mbh_latent_absorb")
+    return qa
+
+
+def attn_latent(qa, ring, positions, q_start, slots, B: int, W: int, H: int, kv_rank: int, rot_dim: int, scale: float, splits: int = 1) -> torch.Tensor:
+    T = qa.shape[0]
+    o = torch.empty(T, H * kv_rank, dtype=qa.dtype, device=qa.device)
+    scratch = torch.empty(T * H * splits * (2 + kv_rank), dtype=torch.float32, device=qa.device) if splits > 1 else None
+    _check(lib().mbh_attn_latent(_ptr(qa), _ptr(ring), _ptr(positions), _ptr(q_start), _ptr(slots), _ptr(o), T, B, W, H, kv_rank, rot_dim, scale,
+                                 splits, _ptr(scratch), dt_of(qa.dtype), _stream()), "mbh_attn_latent")
+    return o
+
+
+def latent_vup(o_lat, w_uv, gate, g_pitch: int, g_off: int, H: int, dv: int, kv_rank: int) -> torch.Tensor:
+    T = o_lat.shape[0]
+    out = torch.empty(T, H * dv, dtype=o_lat.dtype, device=o_lat.device)
+    _check(lib().mbh_latent_vup(_ptr(o_lat), _ptr(w_uv), _ptr(gate), g_pitch, g_off, _ptr(out), T, H, dv, kv_rank, dt_of(o_lat.dtype), _stream()),
+           "mbh_latent_vup")
+    return out

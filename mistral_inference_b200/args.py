@@ -121,18 +121,101 @@ class ClampedGluArgs:
 
 
 @dataclass
+class RotScalingArgs:
+    """YaRN-style frequency scaling of a rotation (rope.scaled_frequencies)."""
+    factor: float
+    original: float
+    fast: float
+    slow: float
+
+
+@dataclass
+class LatentAttentionArgs:
+    """Softmax attention whose queries, keys and values come from per-token latents: the cache keeps the key/value latent
+    (kv_rank) and one rotated key part (rot_dim) shared by the heads.  Each head has `dim` unrotated and `rot_dim` rotated query/key
+    entries and `vdim` value entries; a sigmoid gate per head on the output."""
+    heads: int
+    dim: int
+    rot_dim: int
+    vdim: int
+    q_rank: int
+    kv_rank: int
+    scale: float
+    rot_base: float
+    rot_dims: int
+    rot_scaling: Optional[RotScalingArgs] = None
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "LatentAttentionArgs":
+        rot = d["rot"]
+        sc = rot.get("scaling")
+        a = cls(heads=int(d["heads"]), dim=int(d["dim"]), rot_dim=int(d["rot_dim"]), vdim=int(d["vdim"]), q_rank=int(d["q_rank"]),
+                kv_rank=int(d["kv_rank"]), scale=float(d["scale"]), rot_base=float(rot["base"]), rot_dims=int(rot.get("dims", d["rot_dim"])),
+                rot_scaling=RotScalingArgs(float(sc["factor"]), float(sc["original"]), float(sc["fast"]), float(sc["slow"])) if sc else None)
+        assert a.rot_dims <= a.rot_dim and a.rot_dims % 2 == 0, "the rotation covers an even number of the rotated entries"
+        return a
+
+
+@dataclass
+class MoeFfArgs:
+    """Mixture of gated (SiLU) experts of size `ff`.  The router has experts + identity outputs; the last `identity` of them stand
+    for experts whose output is their input.  Softmax scores; the choice adds a per-output correction and is limited to the best
+    `keep` of `groups` groups of neighbouring outputs; the weights are the chosen outputs' plain scores."""
+    ff: int
+    experts: int
+    top: int
+    identity: int = 0
+    groups: int = 1
+    keep: int = 1
+
+    @property
+    def routed(self) -> int:
+        return self.experts + self.identity
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "MoeFfArgs":
+        r = d["router"]
+        g = r.get("groups") or {}
+        a = cls(ff=int(d["expert"]["ff"]), experts=int(r["experts"]), top=int(r["top"]), identity=int(r.get("identity", 0)),
+                groups=int(g.get("count", 1)), keep=int(g.get("keep", g.get("count", 1))))
+        assert a.routed % a.groups == 0 and 1 <= a.keep <= a.groups, "router groups must be equal and keep <= count"
+        assert a.top <= a.routed // a.groups * a.keep, "more experts per token than the kept groups hold"
+        return a
+
+
+MLP_ARGS = {"dense": ClampedGluArgs, "moe": MoeFfArgs}
+
+
+@dataclass
 class LayerArgs:
-    type: str                                             # "attention" | "lightning"
-    mixer: Union[BiasedAttentionArgs, LightningArgs]
-    mlp: Optional[ClampedGluArgs]
+    type: str                                             # a key of MIXER_ARGS
+    mixer: Union[BiasedAttentionArgs, LightningArgs, LatentAttentionArgs]
+    mlp: Union[None, ClampedGluArgs, MoeFfArgs]
 
 
-MIXER_ARGS = {"attention": BiasedAttentionArgs, "lightning": LightningArgs}
+MIXER_ARGS = {"attention": BiasedAttentionArgs, "lightning": LightningArgs, "latent_attention": LatentAttentionArgs}
+
+
+@dataclass
+class LoopArgs:
+    """Layers start .. stop-1 run `times` times in a row with the same weights (each pass with a cache of its own); before every
+    pass but the first the embedding output is added to the residual stream."""
+    start: int
+    stop: int
+    times: int
+
+
+# What a design fixes (not in config.json): the kind of norm, and whether each sublayer's output is normed again before it is
+# added to the residual stream.
+DESIGNS = {
+    "Fesenex": {"norm": "rms", "post_norm": False},
+    "Taruvik": {"norm": "layer", "post_norm": True},
+}
 
 
 @dataclass
 class LayeredArgs:
-    """config.json of a layered decoder (architecture "Fesenex"): a list of layers, each naming its mixer kind."""
+    """config.json of a layered decoder (an architecture of DESIGNS): a list of layers, each naming its mixer kind."""
     architecture: str
     vocab: int
     width: int
@@ -140,6 +223,17 @@ class LayeredArgs:
     norm_eps: float
     layers: List[LayerArgs]
     max_batch_size: int = 0
+    norm: str = "rms"            # "rms": weight only; "layer": mean removed, weight and bias
+    post_norm: bool = False      # x <- x + norm_b(sublayer(norm(x))) instead of x <- x + sublayer(norm(x))
+    loop: Optional[LoopArgs] = None
+
+    def layer_runs(self) -> List[int]:
+        """The layer index of every layer run, in order (a looped layer appears once per pass)."""
+        n = len(self.layers)
+        if self.loop is None:
+            return list(range(n))
+        lp = self.loop
+        return list(range(lp.start)) + list(range(lp.start, lp.stop)) * lp.times + list(range(lp.stop, n))
 
     @property
     def vocab_size(self) -> int:
@@ -151,7 +245,20 @@ class LayeredArgs:
         for L in d["layers"]:
             if L["type"] not in MIXER_ARGS:
                 raise ValueError(f"unknown mixer type {L['type']!r}")
-            layers.append(LayerArgs(type=L["type"], mixer=MIXER_ARGS[L["type"]].from_dict(L["mixer"]),
-                                    mlp=ClampedGluArgs.from_dict(L["mlp"]) if L.get("mlp") is not None else None))
+            mlp = None
+            if L.get("mlp") is not None:
+                kind = L["mlp"].get("kind", "dense")
+                if kind not in MLP_ARGS:
+                    raise ValueError(f"unknown feed-forward kind {kind!r}")
+                mlp = MLP_ARGS[kind].from_dict(L["mlp"])
+            layers.append(LayerArgs(type=L["type"], mixer=MIXER_ARGS[L["type"]].from_dict(L["mixer"]), mlp=mlp))
+        if d["architecture"] not in DESIGNS:
+            raise ValueError(f"unknown architecture {d['architecture']!r} (known: {sorted(DESIGNS)})")
+        loop = None
+        if d.get("loop"):
+            lp = d["loop"]
+            loop = LoopArgs(int(lp["start"]), int(lp["stop"]), int(lp["times"]))
+            assert 0 <= loop.start < loop.stop <= len(layers) and loop.times >= 1, "loop: 0 <= start < stop <= layers, times >= 1"
         return cls(architecture=d["architecture"], vocab=int(d["vocab"]), width=int(d["width"]),
-                   embedding_scale=float(d["embedding"]["scale"]), norm_eps=float(d["norm"]["eps"]), layers=layers)
+                   embedding_scale=float((d.get("embedding") or {}).get("scale", 1.0)), norm_eps=float(d["norm"]["eps"]), layers=layers,
+                   loop=loop, **DESIGNS[d["architecture"]])

@@ -4,6 +4,8 @@
 #include "hybrid_linear.cuh"
 #include "hybrid_mixers.cuh"
 #include "hybrid_attn_flash.cuh"
+#include "hybrid_latent.cuh"
+#include "hybrid_moe.cuh"
 #include "../../../include/mistral_b200_hybrid.h"
 
 #include <stdio.h>
@@ -40,6 +42,23 @@ static cudaError_t launch_lightning(const LightningArgs& a, cudaStream_t st) {
 
 template <typename T> static void run_embed(const void* tokens, const void* table, float scale, void* x32, int64_t T_, int64_t D, cudaStream_t st) {
     embed_scale_kernel<T><<<(unsigned)T_, 128, 0, st>>>((const int64_t*)tokens, (const T*)table, scale, (float*)x32, (int)D);
+}
+template <typename T> static void run_embed_add(const void* tokens, const void* table, float scale, void* x32, int64_t T_, int64_t D, cudaStream_t st) {
+    embed_scale_kernel<T, true><<<(unsigned)T_, 128, 0, st>>>((const int64_t*)tokens, (const T*)table, scale, (float*)x32, (int)D);
+}
+template <typename T> static void run_layernorm(const void* x32, const void* w, const void* b, void* y, void* acc32, int64_t T_, int64_t D, float eps,
+                                                cudaStream_t st) {
+    const int threads = D >= 1024 ? 256 : 128;
+    if (acc32) layernorm_f32_kernel<T, true><<<(unsigned)T_, threads, 0, st>>>((const float*)x32, (const T*)w, (const T*)b, nullptr, (float*)acc32, (int)D, eps);
+    else layernorm_f32_kernel<T, false><<<(unsigned)T_, threads, 0, st>>>((const float*)x32, (const T*)w, (const T*)b, (T*)y, nullptr, (int)D, eps);
+}
+template <typename T> static void run_attn_wide(const AttnArgs& a, size_t smem, cudaStream_t st) {
+    attn_bias_kernel<T, AT_MAXR_WIDE><<<dim3((unsigned)(a.T * a.H), (unsigned)a.splits), AT_WARPS * 32, smem, st>>>(a);
+    if (a.splits > 1) attn_merge_kernel<T><<<(unsigned)(a.T * a.H), 64, 0, st>>>(a.scratch, (T*)a.out, a.splits, a.e);
+}
+template <typename T> static void run_moe_sparse(const MoeSparseArgs& a, int64_t T_, cudaStream_t st) {
+    moe_gateup_sparse_kernel<T><<<dim3((unsigned)((a.ff + MOE_WARPS - 1) / MOE_WARPS), (unsigned)(T_ * a.top)), MOE_WARPS * 32, 0, st>>>(a);
+    moe_down_sparse_kernel<T><<<dim3((unsigned)((a.width + MOE_WARPS - 1) / MOE_WARPS), (unsigned)T_), MOE_WARPS * 32, 0, st>>>(a);
 }
 template <typename T> static void run_rmsnorm(const void* x32, const void* w, void* y, int64_t T_, int64_t D, float eps, cudaStream_t st) {
     rmsnorm_f32_kernel<T><<<(unsigned)T_, D >= 1024 ? 256 : 128, 0, st>>>((const float*)x32, (const T*)w, (T*)y, (int)D, eps);
@@ -81,7 +100,7 @@ int mbh_rmsnorm(const void* x32, const void* w, void* y, int64_t T, int64_t D, f
 
 int mbh_linear(const void* x, const void* w, const void* bias, void* out, void* out32, int64_t M, int64_t N, int64_t K, int epi, int64_t n_act,
                float limit, float alpha, int dt, void* stream) {
-    if (epi < 0 || epi > 3) return bad("mbh_linear: unknown epilogue");
+    if (epi < 0 || epi > 3) return bad("mbh_linear: unknown epilogue");  // EPI_SWIGLU: mbh_linear_swiglu
     if (epi == EPI_GLU && (N & 1)) return bad("mbh_linear: the gated epilogue needs interleaved (even) rows");
     LinearArgs a{x, w, bias, out, (float*)out32, (int)M, (int)N, (int)K, epi, (int)n_act, limit, alpha};
     cudaError_t e = cudaSuccess;
@@ -150,6 +169,128 @@ int mbh_gated_headnorm(const void* o32, const void* w, const void* g, int64_t g_
     DISPATCH(dt, run_headnorm<ST>(o32, w, g, g_pitch, g_off, y, T, N, eps, st));
     cudaError_t err = cudaGetLastError();
     return err ? fail(err, "mbh_gated_headnorm") : 0;
+}
+
+int mbh_embed_add(const void* tokens, const void* table, float scale, void* x32, int64_t T, int64_t D, int dt, void* stream) {
+    if (T == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, run_embed_add<ST>(tokens, table, scale, x32, T, D, st));
+    cudaError_t e = cudaGetLastError();
+    return e ? fail(e, "mbh_embed_add") : 0;
+}
+
+int mbh_layernorm(const void* x32, const void* w, const void* b, void* y, void* acc32, int64_t T, int64_t D, float eps, int dt, void* stream) {
+    if (T == 0) return 0;
+    if (!y == !acc32) return bad("mbh_layernorm: exactly one of y and acc32");
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, run_layernorm<ST>(x32, w, b, y, acc32, T, D, eps, st));
+    cudaError_t e = cudaGetLastError();
+    return e ? fail(e, "mbh_layernorm") : 0;
+}
+
+int mbh_linear_swiglu(const void* x, const void* w, void* out, int64_t M, int64_t N, int64_t K, const void* rowscale, int64_t rs_pitch,
+                      int64_t rs_group, int dt, void* stream) {
+    if (N & 1) return bad("mbh_linear_swiglu: the gated epilogue needs interleaved (even) rows");
+    if (rowscale && rs_group <= 0) return bad("mbh_linear_swiglu: rs_group must be positive");
+    LinearArgs a{x, w, nullptr, out, nullptr, (int)M, (int)N, (int)K, EPI_SWIGLU, 0, 0.f, 0.f, (const float*)rowscale, (int)rs_pitch, (int)rs_group};
+    cudaError_t e = cudaSuccess;
+    DISPATCH(dt, e = launch_linear<ST>(a, (cudaStream_t)stream));
+    return e ? fail(e, "mbh_linear_swiglu") : 0;
+}
+
+int mbh_swiglu_epilogue(const void* y, void* out, int64_t M, int64_t N, const void* rowscale, int64_t rs_pitch, int64_t rs_group, int dt,
+                        void* stream) {
+    if (N & 1) return bad("mbh_swiglu_epilogue: odd N");
+    if (rowscale && rs_group <= 0) return bad("mbh_swiglu_epilogue: rs_group must be positive");
+    if (M == 0) return 0;
+    LinearArgs a{nullptr, nullptr, nullptr, out, nullptr, (int)M, (int)N, 0, EPI_SWIGLU, 0, 0.f, 0.f, (const float*)rowscale, (int)rs_pitch, (int)rs_group};
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, run_epilogue<ST>(a, y, st));
+    cudaError_t e = cudaGetLastError();
+    return e ? fail(e, "mbh_swiglu_epilogue") : 0;
+}
+
+int mbh_latent_prep(const void* y, const void* qnorm, const void* cnorm, const void* freq, const void* positions, const void* cache_rows, void* cq,
+                    void* ring, int64_t T, int64_t pitch, int64_t q_rank, int64_t kv_rank, int64_t rot_dim, int64_t rot_dims, float eps, float mag,
+                    int dt, void* stream) {
+    if (T == 0) return 0;
+    if (rot_dims > rot_dim || (rot_dims & 1)) return bad("mbh_latent_prep: rot_dims must be even and at most rot_dim");
+    LatentPrepArgs a{y, qnorm, cnorm, (const double*)freq, (const int*)positions, (const int*)cache_rows, cq, ring,
+                     (int)q_rank, (int)kv_rank, (int)rot_dim, (int)rot_dims, (int)pitch, eps, mag};
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, latent_prep_kernel<ST><<<(unsigned)T, 128, 0, st>>>(a));
+    cudaError_t e = cudaGetLastError();
+    return e ? fail(e, "mbh_latent_prep") : 0;
+}
+
+int mbh_latent_absorb(const void* q, const void* w_uk, const void* freq, const void* positions, void* qa, int64_t T, int64_t H, int64_t dn,
+                      int64_t rot_dim, int64_t rot_dims, int64_t kv_rank, float mag, int dt, void* stream) {
+    if (T == 0) return 0;
+    if (rot_dims > rot_dim || (rot_dims & 1)) return bad("mbh_latent_absorb: rot_dims must be even and at most rot_dim");
+    LatentAbsorbArgs a{q, w_uk, (const double*)freq, (const int*)positions, qa, (int)H, (int)dn, (int)rot_dim, (int)rot_dims, (int)kv_rank, mag};
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, latent_absorb_kernel<ST><<<(unsigned)(T * H), 128, sizeof(float) * (size_t)dn, st>>>(a));
+    cudaError_t e = cudaGetLastError();
+    return e ? fail(e, "mbh_latent_absorb") : 0;
+}
+
+int mbh_attn_latent(const void* qa, const void* ring, const void* positions, const void* q_start, const void* slots, void* o_lat, int64_t T,
+                    int64_t B, int64_t W, int64_t H, int64_t kv_rank, int64_t rot_dim, float scale, int64_t splits, void* scratch, int dt,
+                    void* stream) {
+    if (T == 0) return 0;
+    if (kv_rank > 32 * AT_MAXR_WIDE) return bad("mbh_attn_latent: latent size above 512");
+    const int d = (int)(kv_rank + rot_dim);
+    AttnArgs a{qa, ring, ring, nullptr, 0, (const int*)positions, (const int*)q_start, (const int*)slots, o_lat,
+               (int)T, (int)B, (int)W, (int)H, 1, d, (int)kv_rank, scale, (int)(splits > 1 && scratch ? splits : 1), (float*)scratch, d, d};
+    const bool wide = kv_rank > 32 * AT_MAXR;
+    const size_t smem = sizeof(float) * ((size_t)d + AT_WARPS * AT_CHUNK + AT_WARPS * (2 + 32 * (wide ? AT_MAXR_WIDE : AT_MAXR)));
+    cudaStream_t st = (cudaStream_t)stream;
+    if (wide) DISPATCH(dt, run_attn_wide<ST>(a, smem, st));
+    else DISPATCH(dt, run_attn<ST>(a, smem, st));
+    cudaError_t e = cudaGetLastError();
+    return e ? fail(e, "mbh_attn_latent") : 0;
+}
+
+int mbh_latent_vup(const void* o_lat, const void* w_uv, const void* gate, int64_t g_pitch, int64_t g_off, void* out, int64_t T, int64_t H,
+                   int64_t dv, int64_t kv_rank, int dt, void* stream) {
+    if (T == 0) return 0;
+    LatentVupArgs a{o_lat, w_uv, gate, out, (int)H, (int)dv, (int)kv_rank, (int)g_pitch, (int)g_off};
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, latent_vup_kernel<ST><<<(unsigned)(T * H), 128, sizeof(float) * (size_t)kv_rank, st>>>(a));
+    cudaError_t e = cudaGetLastError();
+    return e ? fail(e, "mbh_latent_vup") : 0;
+}
+
+int mbh_moe_route(const void* h, const void* w_router, const void* correction, void* dense, void* idx, void* wsel, int64_t T, int64_t width,
+                  int64_t n, int64_t groups, int64_t keep, int64_t top, int dt, void* stream) {
+    if (T == 0) return 0;
+    if (groups < 1 || n % groups || keep < 1 || keep > groups) return bad("mbh_moe_route: groups must divide the routed outputs, 1 <= keep <= groups");
+    if (top < 1 || top > n / groups * keep) return bad("mbh_moe_route: top exceeds the eligible outputs");
+    const size_t smem = sizeof(float) * (size_t)(2 * n + 2 * groups);
+    if (smem > 48 * 1024) return bad("mbh_moe_route: too many routed outputs");
+    MoeRouteArgs a{h, w_router, correction, (float*)dense, (int*)idx, (float*)wsel, (int)width, (int)n, (int)groups, (int)keep, (int)top};
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, moe_route_kernel<ST><<<(unsigned)T, 128, smem, st>>>(a));
+    cudaError_t e = cudaGetLastError();
+    return e ? fail(e, "mbh_moe_route") : 0;
+}
+
+int mbh_moe_sparse(const void* h, const void* w13, const void* w2, const void* idx, const void* wsel, void* act, void* y32, int64_t T, int64_t width,
+                   int64_t ff, int64_t E, int64_t top, int dt, void* stream) {
+    if (T == 0) return 0;
+    MoeSparseArgs a{h, w13, w2, (const int*)idx, (const float*)wsel, act, (float*)y32, (int)width, (int)ff, (int)E, (int)top};
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, run_moe_sparse<ST>(a, T, st));
+    cudaError_t e = cudaGetLastError();
+    return e ? fail(e, "mbh_moe_sparse") : 0;
+}
+
+int mbh_rows_axpy(void* y32, const void* h, const void* dense, int64_t T, int64_t n, int64_t first, int64_t D, int dt, void* stream) {
+    if (T == 0 || first >= n) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, rows_axpy_kernel<ST><<<(unsigned)T, 128, 0, st>>>((float*)y32, (const ST*)h, (const float*)dense, (int)n, (int)first, (int)D));
+    cudaError_t e = cudaGetLastError();
+    return e ? fail(e, "mbh_rows_axpy") : 0;
 }
 
 }  // extern "C"

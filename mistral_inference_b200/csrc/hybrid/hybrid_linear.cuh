@@ -5,6 +5,9 @@
 //   EPI_GLU       out[M, N/2]: rows of W interleaved (2c = gate, 2c + 1 = up):
 //                 g = min(gate, limit), u = clamp(up, +-limit), out = g * sigmoid(alpha * g) * (u + 1)
 //   EPI_F32       out32[M, N]  = acc + b        (logits)
+//   EPI_SWIGLU    out[M, N/2]: interleaved rows as for EPI_GLU: out = silu(gate) * up * rowscale[m, c / rs_group]
+//                 (rowscale fp32 [M, rs_pitch] or null: a mixture of experts run densely, every expert's hidden units scaled by
+//                 the token's routing weight, 0 for an expert that the token did not choose)
 //
 // In bf16 mode the Linear's own output is rounded to bf16 before the epilogue's arithmetic (the rounding point of a bf16
 // Linear); accumulation is fp32 in both modes.
@@ -18,7 +21,7 @@
 
 namespace mbh {
 
-enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_GLU = 2, EPI_F32 = 3 };
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_GLU = 2, EPI_F32 = 3, EPI_SWIGLU = 4 };
 
 struct LinearArgs {
     const void* x; const void* w; const void* bias;
@@ -26,6 +29,7 @@ struct LinearArgs {
     int M, N, K;
     int epi, n_act;
     float limit, alpha;
+    const float* rowscale; int rs_pitch, rs_group;  // EPI_SWIGLU
 };
 
 template <typename T>
@@ -50,6 +54,13 @@ __device__ __forceinline__ void epilogue_pair(const LinearArgs& a, int m, int n,
         if (!has1) break;
         float g = fminf(v0, a.limit), u = fminf(fmaxf(v1, -a.limit), a.limit);
         static_cast<T*>(a.out)[(size_t)m * (a.N >> 1) + (n >> 1)] = from_f<T>(g * sigmoid_exact(a.alpha * g) * (u + 1.f));
+        break; }
+    case EPI_SWIGLU: {
+        if (!has1) break;
+        const int c = n >> 1;
+        float v = v0 * sigmoid_exact(v0) * v1;
+        if (a.rowscale) v *= a.rowscale[(size_t)m * a.rs_pitch + c / a.rs_group];
+        static_cast<T*>(a.out)[(size_t)m * (a.N >> 1) + c] = from_f<T>(v);
         break; }
     default: {
         float* o = a.out32 + (size_t)m * a.N + n;

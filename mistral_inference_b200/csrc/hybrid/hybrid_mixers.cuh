@@ -2,6 +2,7 @@
 //
 //   embed_scale       x[t] = E[token[t]] * scale                       -> fp32 residual stream
 //   rmsnorm_f32       y = x / sqrt(mean(x^2) + eps) * w                 fp32 in, storage type out
+//   layernorm_f32     y = (x - mean) / sqrt(var + eps) * w + b          fp32 in; storage type out, or added to the residual stream
 //   attn_prep         per-head RMS norm of q and k (shared weight), query temperature by position, value mixing with an
 //                     earlier layer's values, scatter of k and v into the layer's cache ring
 //   attn_bias         causal softmax attention over the ring with a per-(distance, head) additive bias, GQA, separate
@@ -14,11 +15,36 @@
 namespace mbh {
 
 // ------------------------------------------------------------------------------------------------ embedding, norm
-template <typename T>
+template <typename T, bool ADD = false>
 __global__ void embed_scale_kernel(const int64_t* __restrict__ tok, const T* __restrict__ E, float scale, float* __restrict__ x, int D) {
     const T* row = E + (size_t)tok[blockIdx.x] * D;
     float* o = x + (size_t)blockIdx.x * D;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) o[i] = to_f(row[i]) * scale;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        const float v = to_f(row[i]) * scale;
+        o[i] = ADD ? o[i] + v : v;
+    }
+}
+
+// Layer norm of one fp32 row per CTA; the variance is the mean of the squared deviations (second pass over the row, which the
+// first pass left in L1).  ADD: acc[t] += norm(x[t]) in fp32 (the norm after a sublayer, added to the residual stream);
+// otherwise y[t] = norm(x[t]) in the storage type.  b may be null.
+template <typename T, bool ADD>
+__global__ void layernorm_f32_kernel(const float* __restrict__ x, const T* __restrict__ w, const T* __restrict__ b, T* __restrict__ y,
+                                     float* __restrict__ acc, int D, float eps) {
+    __shared__ float red[32];
+    const float* r = x + (size_t)blockIdx.x * D;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) s += r[i];
+    const float mean = block_sum(s, red) / (float)D;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) { const float dlt = r[i] - mean; ss = fmaf(dlt, dlt, ss); }
+    ss = block_sum(ss, red);
+    const float inv = 1.f / sqrtf(ss / (float)D + eps);
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        const float v = (r[i] - mean) * inv * to_f(w[i]) + (b ? to_f(b[i]) : 0.f);
+        if (ADD) acc[(size_t)blockIdx.x * D + i] += v;
+        else y[(size_t)blockIdx.x * D + i] = from_f<T>(v);
+    }
 }
 
 template <typename T>
@@ -99,21 +125,23 @@ struct AttnArgs {
     float scale;
     int splits;             // CTAs per (token, head) along the keys; > 1: partial (max, sum, acc) go to `scratch`
     float* scratch;         // [T*H, splits, 2 + e] fp32
+    int k_pitch, v_pitch;   // elements per ring row of keys / values; 0: G*d / G*e.  (A latent ring is one row per token that both
+                            // pointers address: its first e entries are the value.)  bias_tab may be null: no bias.
 };
 
-constexpr int AT_WARPS = 4, AT_CHUNK = 128, AT_MAXR = 8;  // e <= 32 * AT_MAXR
+constexpr int AT_WARPS = 4, AT_CHUNK = 128, AT_MAXR = 8, AT_MAXR_WIDE = 16;  // e <= 32 * MAXR
 
 // `splits` CTAs per (token, head); their warps take alternate chunks of AT_CHUNK keys (scores: lanes over keys, a whole key row
 // per lane; values: every lane owns ceil(e / 32) adjacent value columns) with a running (max, sum); the warps' partial results
 // are merged through shared memory, the CTAs' (decode: few queries, long contexts) by attn_merge_kernel.
-template <typename T>
+template <typename T, int MAXR = AT_MAXR>
 __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(AttnArgs a) {
     extern __shared__ __align__(16) float sm[];
     const int t = blockIdx.x / a.H, h = blockIdx.x % a.H, g = h / (a.H / a.G);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     float* qs = sm;                                  // [d]
     float* sc = sm + a.d + warp * AT_CHUNK;          // [AT_CHUNK] per warp
-    float* mrg = sm + a.d + AT_WARPS * AT_CHUNK;     // [AT_WARPS][2 + 32 * AT_MAXR]
+    float* mrg = sm + a.d + AT_WARPS * AT_CHUNK;     // [AT_WARPS][2 + 32 * MAXR]
     int b = 0;
     while (b + 1 < a.B && a.q_start[b + 1] <= t) ++b;
     const int pos = a.positions[t], n = pos + 1;
@@ -121,14 +149,14 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(AttnArgs a) {
     for (int i = threadIdx.x; i < a.d; i += blockDim.x) qs[i] = to_f(q[i]) * a.scale;
     __syncthreads();
     const size_t base = (size_t)a.slots[b] * a.W;
-    const T* K = static_cast<const T*>(a.cache_k) + base * a.G * a.d + (size_t)g * a.d;
-    const T* Vp = static_cast<const T*>(a.cache_v) + base * a.G * a.e + (size_t)g * a.e;
-    const size_t ks = (size_t)a.G * a.d, vs = (size_t)a.G * a.e;
+    const size_t ks = a.k_pitch ? (size_t)a.k_pitch : (size_t)a.G * a.d, vs = a.v_pitch ? (size_t)a.v_pitch : (size_t)a.G * a.e;
+    const T* K = static_cast<const T*>(a.cache_k) + base * ks + (size_t)g * a.d;
+    const T* Vp = static_cast<const T*>(a.cache_v) + base * vs + (size_t)g * a.e;
     constexpr int V = Vec<T>::N;
-    const bool vec_ok = (a.d % V == 0) && (reinterpret_cast<uintptr_t>(a.cache_k) % 16 == 0);
-    float m = -INFINITY, l = 0.f, acc[AT_MAXR];
+    const bool vec_ok = (a.d % V == 0) && (ks % V == 0) && (reinterpret_cast<uintptr_t>(a.cache_k) % 16 == 0);
+    float m = -INFINITY, l = 0.f, acc[MAXR];
 #pragma unroll
-    for (int r = 0; r < AT_MAXR; ++r) acc[r] = 0.f;
+    for (int r = 0; r < MAXR; ++r) acc[r] = 0.f;
     const int cpl = (a.e + 31) / 32;  // value columns per lane: lane * cpl .. + cpl - 1
     for (int c0 = (blockIdx.y * AT_WARPS + warp) * AT_CHUNK; c0 < n; c0 += a.splits * AT_WARPS * AT_CHUNK) {
         const int cn = min(AT_CHUNK, n - c0);
@@ -150,8 +178,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(AttnArgs a) {
             } else {
                 for (int i = 0; i < a.d; ++i) s = fmaf(qs[i], to_f(kr[i]), s);
             }
-            const int dist = min(pos - j, a.n_tab - 1);
-            s += a.bias_tab[(size_t)dist * a.H + h];
+            if (a.bias_tab) s += a.bias_tab[(size_t)min(pos - j, a.n_tab - 1) * a.H + h];
             sc[jj] = s;
             cmax = fmaxf(cmax, s);
         }
@@ -165,7 +192,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(AttnArgs a) {
         m = m_new;
         __syncwarp();
 #pragma unroll
-        for (int r = 0; r < AT_MAXR; ++r) acc[r] *= corr;
+        for (int r = 0; r < MAXR; ++r) acc[r] *= corr;
         {
             const T* vp = Vp + lane * cpl;
             int jj = 0;
@@ -176,7 +203,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(AttnArgs a) {
                 const T* r3 = vp + (size_t)((c0 + jj + 3) % a.W) * vs;
                 const float w0 = sc[jj], w1 = sc[jj + 1], w2 = sc[jj + 2], w3 = sc[jj + 3];
 #pragma unroll
-                for (int r = 0; r < AT_MAXR; ++r)
+                for (int r = 0; r < MAXR; ++r)
                     if (r < cpl && lane * cpl + r < a.e)
                         acc[r] += w0 * to_f(r0[r]) + w1 * to_f(r1[r]) + w2 * to_f(r2[r]) + w3 * to_f(r3[r]);
             }
@@ -184,42 +211,42 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(AttnArgs a) {
                 const T* r0 = vp + (size_t)((c0 + jj) % a.W) * vs;
                 const float w0 = sc[jj];
 #pragma unroll
-                for (int r = 0; r < AT_MAXR; ++r)
+                for (int r = 0; r < MAXR; ++r)
                     if (r < cpl && lane * cpl + r < a.e) acc[r] = fmaf(w0, to_f(r0[r]), acc[r]);
             }
         }
         __syncwarp();
     }
     // merge the warps
-    float* mine = mrg + warp * (2 + 32 * AT_MAXR);
+    float* mine = mrg + warp * (2 + 32 * MAXR);
     if (lane == 0) { mine[0] = m; mine[1] = l; }
 #pragma unroll
-    for (int r = 0; r < AT_MAXR; ++r) mine[2 + r * 32 + lane] = acc[r];
+    for (int r = 0; r < MAXR; ++r) mine[2 + r * 32 + lane] = acc[r];
     __syncthreads();
     if (warp == 0) {
         float M = -INFINITY;
-        for (int w = 0; w < AT_WARPS; ++w) M = fmaxf(M, mrg[w * (2 + 32 * AT_MAXR)]);
-        float L = 0.f, o[AT_MAXR];
+        for (int w = 0; w < AT_WARPS; ++w) M = fmaxf(M, mrg[w * (2 + 32 * MAXR)]);
+        float L = 0.f, o[MAXR];
 #pragma unroll
-        for (int r = 0; r < AT_MAXR; ++r) o[r] = 0.f;
+        for (int r = 0; r < MAXR; ++r) o[r] = 0.f;
         for (int w = 0; w < AT_WARPS; ++w) {
-            const float* p = mrg + w * (2 + 32 * AT_MAXR);
+            const float* p = mrg + w * (2 + 32 * MAXR);
             if (p[0] == -INFINITY) continue;
             const float f = expf(p[0] - M);
             L += p[1] * f;
 #pragma unroll
-            for (int r = 0; r < AT_MAXR; ++r) o[r] = fmaf(p[2 + r * 32 + lane], f, o[r]);
+            for (int r = 0; r < MAXR; ++r) o[r] = fmaf(p[2 + r * 32 + lane], f, o[r]);
         }
         if (a.splits > 1) {
             float* part = a.scratch + ((size_t)blockIdx.x * a.splits + blockIdx.y) * (2 + a.e);
             if (lane == 0) { part[0] = M; part[1] = L; }
 #pragma unroll
-            for (int r = 0; r < AT_MAXR; ++r)
+            for (int r = 0; r < MAXR; ++r)
                 if (r < cpl && lane * cpl + r < a.e) part[2 + lane * cpl + r] = o[r];
         } else {
             T* out = static_cast<T*>(a.out) + ((size_t)t * a.H + h) * a.e;
 #pragma unroll
-            for (int r = 0; r < AT_MAXR; ++r)
+            for (int r = 0; r < MAXR; ++r)
                 if (r < cpl && lane * cpl + r < a.e) out[lane * cpl + r] = from_f<T>(o[r] / L);
         }
     }

@@ -1,10 +1,11 @@
 """Layered decoder: a model given as a list of layers, each with its own kind of token mixer (softmax attention with a
-distance bias, lightning attention with a recurrent state, ...) and an optional feed-forward (args.LayeredArgs; architecture
-"Fesenex").  It plugs into the same places as `Transformer`: `from_folder`, `forward(input_ids, seqlens, cache)` over ragged
+distance bias, lightning attention with a recurrent state, latent attention, ...) and an optional feed-forward (gated, or a
+mixture of experts), optionally with a span of layers that runs several times (args.LayeredArgs; architectures "Fesenex",
+"Taruvik").  It plugs into the same places as `Transformer`: `from_folder`, `forward(input_ids, seqlens, cache)` over ragged
 batches, `BufferCache` (per-layer rings and states, `make_cache`), `forward_logprobs` / `next_token_logits` for `generate()`.
 
-On disk: config.json + model.safetensors with tensors `embed`, `l<i>.norm1|norm2`, `l<i>.mix.*`, `l<i>.mlp.gate|up|down`,
-`final.norm`, `head`.  The residual stream is fp32; weights and activations are bf16 or fp32 (`dtype`), the latter in true
+On disk: config.json + model.safetensors with tensors `embed`, `l<i>.norm1|norm2` (and `norm1b|norm2b` with norms after the
+sublayers; a layer norm's bias is the weight's name + `.b`), `l<i>.mix.*`, `l<i>.mlp.*`, `final.norm`, `head`.  The residual stream is fp32; weights and activations are bf16 or fp32 (`dtype`), the latter in true
 fp32 arithmetic.  All compute runs in libmb200_hybrid.so (include/mistral_b200_hybrid.h); CUDA only, no fallback.
 """
 import json
@@ -18,7 +19,7 @@ from torch import nn
 from . import _abi, _abi_hybrid as _h
 from .args import LayeredArgs
 from .cache import BufferCache, CacheInputMetadata
-from .transformer_layers import MIXERS, BiasedAttention, ClampedGLU, LayeredBlock, LightningMixer
+from .transformer_layers import FEED_FORWARDS, MIXERS, BiasedAttention, LayeredBlock, LightningMixer, Norm
 
 
 class LayeredTransformer(nn.Module):
@@ -27,6 +28,7 @@ class LayeredTransformer(nn.Module):
         self.args = args
         self.vocab_size = args.vocab
         self.n_layers = self.n_local_layers = len(args.layers)
+        self.runs = args.layer_runs()  # layer index of every layer run; each run has its own cache entry
         self.embed = nn.Parameter(torch.empty(args.vocab, args.width), requires_grad=False)
         blocks = []
         seen_vmix = False
@@ -36,9 +38,10 @@ class LayeredTransformer(nn.Module):
                 seen_vmix = seen_vmix or L.mixer.v_mix
             else:
                 mixer = MIXERS[L.type](args.width, L.mixer, args.norm_eps)
-            blocks.append(LayeredBlock(args.width, args.norm_eps, mixer, ClampedGLU(args.width, L.mlp) if L.mlp is not None else None))
+            mlp = FEED_FORWARDS[type(L.mlp)](args.width, L.mlp) if L.mlp is not None else None
+            blocks.append(LayeredBlock(args.width, args.norm_eps, mixer, mlp, norm=args.norm, post_norm=args.post_norm))
         self.layers = nn.ModuleList(blocks)
-        self.final_norm = nn.Parameter(torch.empty(args.width), requires_grad=False)
+        self.final_norm = Norm(args.width, args.norm_eps, args.norm)
         self.head = nn.Parameter(torch.empty(args.vocab, args.width), requires_grad=False)
         self.last_argmax: Optional[torch.Tensor] = None
 
@@ -52,9 +55,10 @@ class LayeredTransformer(nn.Module):
         return self.embed.device
 
     def make_cache(self, max_batch_size: int, max_seq_len: int) -> BufferCache:
-        """The cache of this model: a whole-sequence ring per attention layer, an fp32 state per lightning layer."""
-        specs = [blk.mix.cache_spec() for blk in self.layers]
-        cache = BufferCache(self.n_layers, max_batch_size, max_seq_len, 0, 0, None, layer_specs=specs)
+        """The cache of this model, one entry per layer RUN (a layer that runs in several passes keeps each pass's keys apart): a
+        whole-sequence ring per attention layer, an fp32 state per lightning layer."""
+        specs = [self.layers[i].mix.cache_spec() for i in self.runs]
+        cache = BufferCache(len(specs), max_batch_size, max_seq_len, 0, 0, None, layer_specs=specs)
         cache.to(device=self.device, dtype=self.dtype)
         cache.reset()
         return cache
@@ -86,17 +90,23 @@ class LayeredTransformer(nn.Module):
     def _run_layers(self, input_ids: torch.Tensor, md: List[CacheInputMetadata], cache: BufferCache) -> torch.Tensor:
         x = _h.embed_scale(input_ids, self.embed, self.args.embedding_scale)
         ctx: Dict[str, torch.Tensor] = {}
-        for i, blk in enumerate(self.layers):
-            blk(x, cache.get_view(i, md[i]), ctx)
+        lp = self.args.loop
+        first_pass = True
+        for r, i in enumerate(self.runs):
+            if lp is not None and i == lp.start:
+                if not first_pass:  # every pass but the first starts from the stream plus the embedding output
+                    _h.embed_add(input_ids, self.embed, self.args.embedding_scale, x)
+                first_pass = False
+            self.layers[i](x, cache.get_view(r, md[r]), ctx)
             if self._tap is not None:
-                self._tap(i, x)
+                self._tap(r, x)
         return x
 
-    _tap = None  # debugging hook: called with (layer, residual stream) after every layer
+    _tap = None  # debugging hook: called with (layer run, residual stream) after every layer run
 
     def logits_of(self, x32: torch.Tensor) -> torch.Tensor:
         """Final norm + head, fp32 [rows, vocab]."""
-        return _h.linear(_h.rmsnorm(x32, self.final_norm, self.args.norm_eps), self.head, epi=_h.EPI_F32)
+        return _h.linear(self.final_norm(x32), self.head, epi=_h.EPI_F32)
 
     def _graph_decode_ok(self, seqlens: List[int], cache: Optional[BufferCache]) -> bool:
         if cache is None or self._tap is not None or os.environ.get("MB200_DECODE_GRAPH", "1") == "0":
@@ -183,26 +193,27 @@ class LayeredTransformer(nn.Module):
         if k == "embed":
             return put(self.embed)
         if k == "final.norm":
-            return put(self.final_norm)
+            return put(self.final_norm.weight)
+        if k == "final.norm.b" and self.final_norm.bias is not None:
+            return put(self.final_norm.bias)
         if k == "head":
             return put(self.head)
         lid, rest = k.split(".", 1)
         assert lid[0] == "l" and lid[1:].isdigit() and int(lid[1:]) < self.n_layers, f"Unexpected key {k}"
         blk: LayeredBlock = self.layers[int(lid[1:])]  # type: ignore[assignment]
-        if rest == "norm1":
-            return put(blk.norm1)
-        if rest == "norm2" and blk.norm2 is not None:
-            return put(blk.norm2)
-        part, name = rest.split(".", 1)
-        if part == "mlp" and blk.mlp is not None:
-            ff = blk.mlp
-            if name == "gate":
-                return put(ff.w13.view(ff.a.ff, 2, ff.width)[:, 0])
-            if name == "up":
-                return put(ff.w13.view(ff.a.ff, 2, ff.width)[:, 1])
-            if name == "down":
-                return put(ff.w2)
+        base = rest[:-2] if rest.endswith(".b") else rest
+        if base in ("norm1", "norm2", "norm1b", "norm2b") and getattr(blk, base) is not None:
+            nrm: Norm = getattr(blk, base)
+            if base == rest:
+                return put(nrm.weight)
+            if nrm.bias is not None:
+                return put(nrm.bias)
+        part, name = rest.split(".", 1) if "." in rest else (rest, "")
+        if part == "mlp" and blk.mlp is not None and blk.mlp.assign(name, put):
+            return None
         m = blk.mix
+        if part == "mix" and hasattr(m, "assign") and m.assign(name, put):
+            return None
         if part == "mix" and isinstance(m, BiasedAttention):
             spans = {"q": (0, m.nq), "k": (m.nq, m.nq + m.nk), "v": (m.nq + m.nk, m.nq + m.nk + m.nv)}
             if name in spans:
@@ -227,16 +238,22 @@ class LayeredTransformer(nn.Module):
         raise ValueError(f"Unexpected key {k}")
 
     def checkpoint_keys(self) -> List[str]:
-        keys = ["embed", "final.norm", "head"]
+        def norm_keys(name: str, nrm: Optional[Norm]) -> List[str]:
+            return [] if nrm is None else [name] + ([name + ".b"] if nrm.bias is not None else [])
+
+        keys = ["embed", "head"] + norm_keys("final.norm", self.final_norm)
         for i, blk in enumerate(self.layers):
             p = f"l{i}."
-            keys.append(p + "norm1")
+            for n in ("norm1", "norm1b", "norm2", "norm2b"):
+                keys += norm_keys(p + n, getattr(blk, n))
             if isinstance(blk.mix, BiasedAttention):
                 keys += [p + "mix." + n for n in ("q", "q.b", "k", "k.b", "v", "v.b", "q.norm", "k.norm", "rel", "vmix", "o")]
-            else:
+            elif isinstance(blk.mix, LightningMixer):
                 keys += [p + "mix." + n for n in ("q", "k", "v", "g", "norm", "o")]
+            else:
+                keys += [p + "mix." + n for n in blk.mix.checkpoint_names()]
             if blk.mlp is not None:
-                keys += [p + "norm2", p + "mlp.gate", p + "mlp.up", p + "mlp.down"]
+                keys += [p + "mlp." + n for n in blk.mlp.checkpoint_names()]
         return keys
 
     def load_state_dict(self, state_dict: Any, strict: bool = True, assign: bool = False) -> None:  # type: ignore[override]

@@ -191,11 +191,40 @@ import math  # noqa: E402
 from typing import Dict  # noqa: E402
 
 from . import _abi_hybrid as _h  # noqa: E402
-from .args import BiasedAttentionArgs, ClampedGluArgs, LightningArgs  # noqa: E402
+from .args import BiasedAttentionArgs, ClampedGluArgs, LatentAttentionArgs, LightningArgs, MoeFfArgs  # noqa: E402
+from .rope import scaled_frequencies  # noqa: E402
 from .cache import LayerCacheSpec  # noqa: E402
 
 
 FLASH_MIN_QUERIES = 16  # prompts (portions) at least this long take the tensor-core attention kernel in bf16
+MOE_SPARSE_MAX_TOKENS = 16  # up to this many tokens a mixture of experts streams only the chosen experts' weights
+
+
+class Norm(nn.Module):
+    """The norm of a layered decoder: "rms" (weight) or "layer" (mean removed; weight and bias).  Reads the fp32 residual stream (or
+    an fp32 sublayer output) and either returns the normed rows in the model dtype or adds them, in fp32, to `add_to`."""
+
+    def __init__(self, width: int, eps: float, kind: str):
+        super().__init__()
+        assert kind in ("rms", "layer"), kind
+        self.kind, self.eps = kind, eps
+        self.weight = nn.Parameter(torch.empty(width), requires_grad=False)
+        self.bias = nn.Parameter(torch.empty(width), requires_grad=False) if kind == "layer" else None
+
+    def forward(self, x32: torch.Tensor, add_to: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if self.kind == "layer":
+            return _h.layernorm(x32, self.weight, self.bias, self.eps, add_to=add_to)
+        assert add_to is None, "an rms norm after the sublayer is not built"
+        return _h.rmsnorm(x32, self.weight, self.eps)
+
+
+def project_out(y: torch.Tensor, w: torch.Tensor, x32: torch.Tensor, post: Optional[Norm]) -> None:
+    """The last Linear of a sublayer: added to the fp32 residual stream by its epilogue, or, when the block norms the sublayer's
+    output first (`post`), written in fp32 and added by the norm kernel."""
+    if post is None:
+        _h.linear(y, w, epi=_h.EPI_RESIDUAL, residual=x32)
+    else:
+        post(_h.linear(y, w, epi=_h.EPI_F32), add_to=x32)
 
 
 def distance_buckets(rows: int, far: float) -> List[int]:
@@ -241,7 +270,7 @@ class BiasedAttention(nn.Module):
             self._bias_tab = self.rel.float().index_select(0, idx).contiguous()
         return self._bias_tab
 
-    def run(self, hn: torch.Tensor, x32: torch.Tensor, view: CacheView, ctx: Dict[str, torch.Tensor]) -> None:
+    def run(self, hn: torch.Tensor, x32: torch.Tensor, view: CacheView, ctx: Dict[str, torch.Tensor], post: Optional[Norm] = None) -> None:
         a, md = self.a, view.metadata
         T = hn.shape[0]
         qkv = _h.linear(hn, self.wqkv, self.bqkv)
@@ -261,7 +290,7 @@ class BiasedAttention(nn.Module):
                      a.heads, a.kv_heads, a.dim, a.vdim, a.scale,
                      n_tiles=sum((n + 63) // 64 for n in md.seqlens) if md.max_seqlen >= FLASH_MIN_QUERIES else 0,
                      splits=_h.attn_splits(T, a.heads, md.window))
-        _h.linear(out, self.wo, epi=_h.EPI_RESIDUAL, residual=x32)
+        project_out(out, self.wo, x32, post)
 
 
 class LightningMixer(nn.Module):
@@ -280,14 +309,14 @@ class LightningMixer(nn.Module):
     def cache_spec(self) -> LayerCacheSpec:
         return LayerCacheSpec(kind="state", state_shape=(self.a.heads, self.a.dim, self.a.vdim))
 
-    def run(self, hn: torch.Tensor, x32: torch.Tensor, view: CacheView, ctx: Dict[str, torch.Tensor]) -> None:
+    def run(self, hn: torch.Tensor, x32: torch.Tensor, view: CacheView, ctx: Dict[str, torch.Tensor], post: Optional[Norm] = None) -> None:
         a, md = self.a, view.metadata
         T = hn.shape[0]
         qkvg = _h.linear(hn, self.wqkvg, n_act=2 * self.nqk + self.nv)
         o32 = torch.empty(T, self.nv, dtype=torch.float32, device=hn.device)
         _h.lightning_scan(qkvg, view.state, self.decay, md.q_start, md.seqpos, md.slots, o32, len(md.seqlens), a.heads, a.dim, a.vdim)
         y = _h.gated_headnorm(o32, self.norm, qkvg, qkvg.shape[1], 2 * self.nqk + self.nv, self.eps)
-        _h.linear(y, self.wo, epi=_h.EPI_RESIDUAL, residual=x32)
+        project_out(y, self.wo, x32, post)
 
 
 class ClampedGLU(nn.Module):
@@ -300,27 +329,160 @@ class ClampedGLU(nn.Module):
         self.w13 = nn.Parameter(torch.empty(2 * a.ff, width), requires_grad=False)
         self.w2 = nn.Parameter(torch.empty(width, a.ff), requires_grad=False)
 
-    def run(self, hn: torch.Tensor, x32: torch.Tensor) -> None:
+    def run(self, hn: torch.Tensor, x32: torch.Tensor, post: Optional[Norm] = None) -> None:
         y = _h.linear(hn, self.w13, epi=_h.EPI_GLU, limit=self.a.limit, alpha=self.a.alpha)
-        _h.linear(y, self.w2, epi=_h.EPI_RESIDUAL, residual=x32)
+        project_out(y, self.w2, x32, post)
+
+    def checkpoint_names(self) -> List[str]:
+        return ["gate", "up", "down"]
+
+    def assign(self, name: str, put) -> bool:
+        if name == "gate":
+            put(self.w13.view(self.a.ff, 2, self.width)[:, 0])
+        elif name == "up":
+            put(self.w13.view(self.a.ff, 2, self.width)[:, 1])
+        elif name == "down":
+            put(self.w2)
+        else:
+            return False
+        return True
 
 
-MIXERS = {"attention": BiasedAttention, "lightning": LightningMixer}
+class LatentAttention(nn.Module):
+    """Causal softmax attention through latents (args.LatentAttentionArgs).  With h the normed input:
+        c_q = rms(W_dq h) * n_q,  q = W_uq c_q  (per head [dim plain | rot_dim rotated]);
+        [c' | k_r] = W_dkv h,  c = rms(c') * n_c;   k_h = [W_uk,h c | rot(k_r)],  v_h = W_uv,h c;
+        out = W_o concat_h( sigmoid(W_g h)_h * softmax(q_h . k_h * scale) v_h ).
+    The ring holds one row [c | rot(k_r)] per token.  Attention runs on the rows themselves: W_uk is folded into the query
+    (q_h . W_uk,h c = (W_uk,h^T q_h) . c) and W_uv is applied to the attention-weighted sum of latents, so a decode step reads
+    kv_rank + rot_dim numbers per cached token, whatever the number of heads.  Packed weights: w_in = dq ++ dkv ++ g rows."""
+
+    def __init__(self, width: int, a: LatentAttentionArgs, eps: float):
+        super().__init__()
+        self.a, self.eps = a, eps
+        self.n_in = a.q_rank + a.kv_rank + a.rot_dim + a.heads
+        self.w_in = nn.Parameter(torch.empty(self.n_in, width), requires_grad=False)
+        self.q_norm = nn.Parameter(torch.empty(a.q_rank), requires_grad=False)
+        self.c_norm = nn.Parameter(torch.empty(a.kv_rank), requires_grad=False)
+        self.w_uq = nn.Parameter(torch.empty(a.heads * (a.dim + a.rot_dim), a.q_rank), requires_grad=False)
+        self.w_uk = nn.Parameter(torch.empty(a.heads * a.dim, a.kv_rank), requires_grad=False)
+        self.w_uv = nn.Parameter(torch.empty(a.heads * a.vdim, a.kv_rank), requires_grad=False)
+        self.wo = nn.Parameter(torch.empty(width, a.heads * a.vdim), requires_grad=False)
+        self._freq: Optional[torch.Tensor] = None
+        self._mag = 1.0
+
+    def cache_spec(self) -> LayerCacheSpec:
+        # one shared "head" whose key row is the latent row; the values are its first kv_rank entries, so no value ring
+        return LayerCacheSpec(kind="ring", n_kv_heads=1, k_dim=self.a.kv_rank + self.a.rot_dim, v_dim=0, window=None)
+
+    def frequencies(self) -> torch.Tensor:
+        if self._freq is None or self._freq.device != self.wo.device:
+            f, self._mag = scaled_frequencies(self.a.rot_dims, self.a.rot_base, self.a.rot_scaling)
+            self._freq = f.to(self.wo.device)
+        return self._freq
+
+    def run(self, hn: torch.Tensor, x32: torch.Tensor, view: CacheView, ctx: Dict[str, torch.Tensor], post: Optional[Norm] = None) -> None:
+        a, md = self.a, view.metadata
+        T = hn.shape[0]
+        freq = self.frequencies()
+        y = _h.linear(hn, self.w_in)
+        cq = _h.latent_prep(y, self.q_norm, self.c_norm, freq, md.positions, md.cache_rows, view.cache_k, a.q_rank, a.kv_rank, a.rot_dim,
+                            a.rot_dims, self.eps, self._mag)
+        q = _h.linear(cq, self.w_uq)
+        qa = _h.latent_absorb(q, self.w_uk, freq, md.positions, a.heads, a.dim, a.rot_dim, a.rot_dims, a.kv_rank, self._mag)
+        o_lat = _h.attn_latent(qa, view.cache_k, md.positions, md.q_start, md.slots, len(md.seqlens), md.window, a.heads, a.kv_rank, a.rot_dim,
+                               a.scale, splits=_h.attn_splits(T, a.heads, md.window))
+        out = _h.latent_vup(o_lat, self.w_uv, y, self.n_in, a.q_rank + a.kv_rank + a.rot_dim, a.heads, a.vdim, a.kv_rank)
+        project_out(out, self.wo, x32, post)
+
+    def checkpoint_names(self) -> List[str]:
+        return ["dq", "dq.norm", "uq", "dkv", "dkv.norm", "uk", "uv", "g", "o"]
+
+    def assign(self, name: str, put) -> bool:
+        a = self.a
+        o1, o2 = a.q_rank, a.q_rank + a.kv_rank + a.rot_dim
+        targets = {"dq": lambda: self.w_in[:o1], "dkv": lambda: self.w_in[o1:o2], "g": lambda: self.w_in[o2:], "dq.norm": lambda: self.q_norm,
+                   "dkv.norm": lambda: self.c_norm, "uq": lambda: self.w_uq, "uk": lambda: self.w_uk, "uv": lambda: self.w_uv, "o": lambda: self.wo}
+        if name not in targets:
+            return False
+        put(targets[name]())
+        return True
+
+
+class MoeFeedForward(nn.Module):
+    """Mixture of gated experts with an fp32 softmax router (args.MoeFfArgs).  Packed weights: w13 [E * 2 * ff, width], expert after
+    expert with gate and up rows interleaved; w2 [width, E * ff], expert e's down projection in columns e*ff ..; identity experts have
+    no weights.  Few tokens (decode) stream the chosen experts only; prompts run all experts as two Linears, the first one's
+    epilogue scaling every expert's hidden units by the token's routing weight (0 when not chosen)."""
+
+    def __init__(self, width: int, a: MoeFfArgs):
+        super().__init__()
+        self.a, self.width = a, width
+        self.router = nn.Parameter(torch.empty(a.routed, width), requires_grad=False)
+        self.correction = nn.Parameter(torch.empty(a.routed), requires_grad=False)
+        self.w13 = nn.Parameter(torch.empty(a.experts * 2 * a.ff, width), requires_grad=False)
+        self.w2 = nn.Parameter(torch.empty(width, a.experts * a.ff), requires_grad=False)
+        self.sparse_max_tokens = MOE_SPARSE_MAX_TOKENS
+
+    def run(self, hn: torch.Tensor, x32: torch.Tensor, post: Optional[Norm] = None) -> None:
+        a = self.a
+        dense, idx, wsel = _h.moe_route(hn, self.router, self.correction, a.groups, a.keep, a.top)
+        if hn.shape[0] <= self.sparse_max_tokens:
+            y32 = _h.moe_sparse(hn, self.w13, self.w2, idx, wsel, a.experts, a.ff)
+        else:
+            act = _h.linear_swiglu(hn, self.w13, rowscale=dense, group=a.ff)
+            y32 = _h.linear(act, self.w2, epi=_h.EPI_F32)
+            if a.identity:
+                _h.rows_axpy(y32, hn, dense, a.experts)
+        if post is None:
+            x32.add_(y32)
+        else:
+            post(y32, add_to=x32)
+
+    def checkpoint_names(self) -> List[str]:
+        return ["router", "correction"] + [f"e{e}.{n}" for e in range(self.a.experts) for n in ("gate", "up", "down")]
+
+    def assign(self, name: str, put) -> bool:
+        a = self.a
+        if name == "router":
+            put(self.router)
+        elif name == "correction":
+            put(self.correction)
+        elif name[0] == "e" and "." in name and name[1:name.index(".")].isdigit() and int(name[1:name.index(".")]) < a.experts:
+            e, part = int(name[1:name.index(".")]), name[name.index(".") + 1:]
+            if part == "gate":
+                put(self.w13.view(a.experts, a.ff, 2, self.width)[e, :, 0])
+            elif part == "up":
+                put(self.w13.view(a.experts, a.ff, 2, self.width)[e, :, 1])
+            elif part == "down":
+                put(self.w2.view(self.width, a.experts, a.ff)[:, e])
+            else:
+                return False
+        else:
+            return False
+        return True
+
+
+MIXERS = {"attention": BiasedAttention, "lightning": LightningMixer, "latent_attention": LatentAttention}
+FEED_FORWARDS = {ClampedGluArgs: ClampedGLU, MoeFfArgs: MoeFeedForward}
 
 
 class LayeredBlock(nn.Module):
-    """x <- x + mixer(norm1(x)); x <- x + ff(norm2(x)) when the layer has a feed-forward.  `x32` is updated in place."""
+    """x <- x + mixer(norm1(x)); x <- x + ff(norm2(x)) when the layer has a feed-forward; with `post_norm` each sublayer's output
+    goes through a norm of its own (norm1b, norm2b) before it is added.  `x32` is updated in place."""
 
-    def __init__(self, width: int, eps: float, mixer: nn.Module, mlp: Optional[ClampedGLU]):
+    def __init__(self, width: int, eps: float, mixer: nn.Module, mlp: Optional[nn.Module], norm: str = "rms", post_norm: bool = False):
         super().__init__()
         self.eps = eps
-        self.norm1 = nn.Parameter(torch.empty(width), requires_grad=False)
+        self.norm1 = Norm(width, eps, norm)
+        self.norm1b = Norm(width, eps, norm) if post_norm else None
         self.mix = mixer
         self.mlp = mlp
-        self.norm2 = nn.Parameter(torch.empty(width), requires_grad=False) if mlp is not None else None
+        self.norm2 = Norm(width, eps, norm) if mlp is not None else None
+        self.norm2b = Norm(width, eps, norm) if mlp is not None and post_norm else None
 
     def forward(self, x32: torch.Tensor, view: CacheView, ctx: Dict[str, torch.Tensor]) -> torch.Tensor:
-        self.mix.run(_h.rmsnorm(x32, self.norm1, self.eps), x32, view, ctx)
+        self.mix.run(self.norm1(x32), x32, view, ctx, self.norm1b)
         if self.mlp is not None:
-            self.mlp.run(_h.rmsnorm(x32, self.norm2, self.eps), x32)
+            self.mlp.run(self.norm2(x32), x32, self.norm2b)
         return x32
