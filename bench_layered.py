@@ -1,7 +1,8 @@
-"""`bench.py --design fesenex`: prefill and decode throughput of the layered decoder at layer sizes of real models (random
+"""`bench.py --design fesenex|taruvik`: prefill and decode throughput of the layered decoder at layer sizes of real models (random
 weights), beside the dense `Transformer` of equal width / heads / feed-forward size / depth / vocabulary, plus the time of each
 hybrid kernel at those shapes against its roofline (bf16 tensor peak or HBM copy bandwidth from MEASURED_PEAKS.json).
-Timed with CUDA events after warm-up; the prompt batch and the weights exceed L2 at the larger size, and L2 is flushed between
+For `taruvik` (latent attention, mixture of experts) the neighbour is the `Transformer` with a mixture of experts of equal
+width / heads / experts / depth.  Timed with CUDA events after warm-up; the prompt batch and the weights exceed L2 at the larger size, and L2 is flushed between
 timed kernel launches.  Prints one JSON line."""
 import json
 import math
@@ -162,7 +163,172 @@ def kernel_table(s: dict, T: int, ctx: int, peaks: dict, dev) -> dict:
     return rows
 
 
+# ----------------------------------------------------------------------------------------------- Taruvik
+TARUVIK_SIZES = {
+    "w2048": dict(width=2048, heads=16, dim=128, rot_dim=64, vdim=128, q_rank=768, kv_rank=512, experts=16, identity=4, top=4, groups=4, keep=2,
+                  ff=1408, vocab=32768, layers=4),
+    "w4096": dict(width=4096, heads=32, dim=128, rot_dim=64, vdim=128, q_rank=1536, kv_rank=512, experts=8, identity=0, top=2, groups=1, keep=1,
+                  ff=14336, vocab=32768, layers=2),
+}
+
+
+def taruvik_config(s: dict) -> dict:
+    mix = {"heads": s["heads"], "dim": s["dim"], "rot_dim": s["rot_dim"], "vdim": s["vdim"], "q_rank": s["q_rank"], "kv_rank": s["kv_rank"],
+           "scale": (s["dim"] + s["rot_dim"]) ** -0.5,
+           "rot": {"base": 10000.0, "dims": s["rot_dim"], "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    mlp = {"kind": "moe", "expert": {"ff": s["ff"]},
+           "router": {"experts": s["experts"], "identity": s["identity"], "top": s["top"], "groups": {"count": s["groups"], "keep": s["keep"]}}}
+    return {"architecture": "Taruvik", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5},
+            "layers": [{"type": "latent_attention", "mixer": mix, "mlp": mlp} for _ in range(s["layers"])]}
+
+
+def build_taruvik(s: dict, dev):
+    from mistral_inference_b200.args import LayeredArgs
+    from mistral_inference_b200.layered import LayeredTransformer
+
+    m = LayeredTransformer.empty(LayeredArgs.from_dict(taruvik_config(s)), dev, torch.bfloat16)
+    g = torch.Generator(device=dev).manual_seed(0)
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if p.dim() >= 2:
+                p.copy_(torch.randn(p.shape, generator=g, device=dev, dtype=torch.float32) / math.sqrt(p.shape[-1]))
+            elif n.endswith("weight") or "norm" in n.rsplit(".", 1)[-1]:
+                p.fill_(1.0)
+            else:
+                p.copy_(torch.randn(p.shape, generator=g, device=dev, dtype=torch.float32) * 0.01)
+    return m.eval()
+
+
+def build_moe_transformer(s: dict, dev):
+    import mistral_inference_b200 as mi
+    from mistral_inference_b200.args import MoeArgs
+    from mistral_inference_b200.transformer import Transformer
+
+    args = mi.TransformerArgs(dim=s["width"], n_layers=s["layers"], head_dim=s["dim"], hidden_dim=s["ff"], n_heads=s["heads"], n_kv_heads=s["heads"],
+                              norm_eps=1e-5, vocab_size=s["vocab"], max_batch_size=8, moe=MoeArgs(num_experts=s["experts"], num_experts_per_tok=s["top"]))
+    m = Transformer.empty(args, dev, torch.bfloat16)
+    g = torch.Generator(device=dev).manual_seed(0)
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if p.dim() >= 2:
+                p.copy_(torch.randn(p.shape, generator=g, device=dev, dtype=torch.float32) / math.sqrt(p.shape[-1]))
+            else:
+                p.fill_(1.0)
+    return m.eval()
+
+
+def taruvik_kernel_table(s: dict, T: int, ctx: int, peaks: dict, dev) -> dict:
+    """Every kernel that the design added, alone at this size: time, achieved rate, fraction of the measured roofline (bytes and
+    FLOPs are the algorithm's: what a perfect kernel would have to move or compute)."""
+    from mistral_inference_b200 import _abi_hybrid as h
+    from mistral_inference_b200.cache import BufferCache, LayerCacheSpec
+    from mistral_inference_b200.rope import scaled_frequencies
+
+    bf = torch.bfloat16
+    W, H, dn, dr, dv, rq, rk, E, ff, top = (s[k] for k in ("width", "heads", "dim", "rot_dim", "vdim", "q_rank", "kv_rank", "experts", "ff", "top"))
+    n_routed = E + s["identity"]
+    flush = torch.zeros(160 << 20, dtype=torch.float32, device=dev)
+    rows = {}
+
+    def rec(name, ms, flops=0.0, bytes_=0.0, note=None):
+        r = {"ms": round(ms, 4)}
+        if flops:
+            r["tflops"] = round(flops / ms / 1e9, 1)
+            r["of_bf16_peak"] = round(flops / ms / 1e9 / peaks["bf16_tflops"], 3)
+        if bytes_:
+            r["gb_s"] = round(bytes_ / ms / 1e6, 1)
+            r["of_hbm_peak"] = round(bytes_ / ms / 1e6 / peaks["hbm_gbs"], 3)
+        if note:
+            r["note"] = note
+        rows[name] = r
+
+    B = 8
+    x32 = torch.randn(T, W, device=dev)
+    wv, bv = torch.ones(W, device=dev).to(bf), torch.zeros(W, device=dev).to(bf)
+    rec("layernorm prompt", _time(lambda: h.layernorm(x32, wv, bv, 1e-5), 3, 8, flush), bytes_=T * W * 6.0)
+    acc = torch.zeros(T, W, device=dev)
+    rec("layernorm + residual add prompt", _time(lambda: h.layernorm(x32, wv, bv, 1e-5, add_to=acc), 3, 8, flush), bytes_=T * W * 12.0)
+    # latent attention
+    freq, mag = scaled_frequencies(dr, 10000.0, None)
+    freq = freq.to(dev)
+    n_in = rq + rk + dr + H
+    cache = BufferCache(1, B, ctx + 8, 0, 0, None, layer_specs=[LayerCacheSpec(kind="ring", n_kv_heads=1, k_dim=rk + dr, v_dim=0)]).to(dev, bf)
+    cache.cache_k[0].normal_()
+    md = cache.get_input_metadata([T])[0]
+    y = torch.randn(T, n_in, device=dev).to(bf)
+    qn, cn = torch.ones(rq, device=dev).to(bf), torch.ones(rk, device=dev).to(bf)
+    rec("latent_prep prompt", _time(lambda: h.latent_prep(y, qn, cn, freq, md.positions, md.cache_rows, cache.cache_k[0], rq, rk, dr, dr, 1e-5, mag), 3, 8, flush),
+        bytes_=T * (n_in + rq + rk + dr) * 2.0)
+    q = torch.randn(T, H * (dn + dr), device=dev).to(bf)
+    w_uk = (torch.randn(H * dn, rk, device=dev) / math.sqrt(rk)).to(bf)
+    rec("latent_absorb prompt", _time(lambda: h.latent_absorb(q, w_uk, freq, md.positions, H, dn, dr, dr, rk, mag), 2, 5, flush), flops=2.0 * T * H * dn * rk)
+    qa = torch.randn(T, H * (rk + dr), device=dev).to(bf)
+    Tp = min(T, 1024)  # the exact kernel on a prompt: a shorter one keeps the run short
+    mdp = cache.get_input_metadata([Tp])[0]
+    qp = qa[:Tp].contiguous()
+    rec(f"attn_latent prompt T={Tp}", _time(lambda: h.attn_latent(qp, cache.cache_k[0], mdp.positions, mdp.q_start, mdp.slots, 1, ctx + 8, H, rk, dr, 0.07,
+                                                                 splits=h.attn_splits(Tp, H, ctx + 8)), 1, 3, flush),
+        flops=2.0 * H * (2 * rk + dr) * Tp * (Tp + 1) / 2, note="exact fp32 FMA kernel, no tensor cores")
+    cache.reset(); cache.init_kvseqlens(B); cache.update_seqlens([ctx] * B)
+    md2 = cache.get_input_metadata([1] * B)[0]
+    q2 = qa[:B].contiguous()
+    rec(f"attn_latent decode B={B} ctx={ctx}", _time(lambda: h.attn_latent(q2, cache.cache_k[0], md2.positions, md2.q_start, md2.slots, B, ctx + 8, H, rk, dr, 0.07,
+                                                                            splits=h.attn_splits(B, H, ctx + 8)), 3, 8, flush),
+        bytes_=B * (ctx + 1) * (rk + dr) * 2.0, note="bytes: every latent row once; each head's CTAs re-read them through L2")
+    o_lat = torch.randn(T, H * rk, device=dev).to(bf)
+    w_uv = (torch.randn(H * dv, rk, device=dev) / math.sqrt(rk)).to(bf)
+    rec("latent_vup prompt", _time(lambda: h.latent_vup(o_lat, w_uv, y, n_in, rq + rk + dr, H, dv, rk), 2, 5, flush), flops=2.0 * T * H * dv * rk)
+    ob = o_lat[:B].contiguous()
+    rec(f"latent_vup decode B={B}", _time(lambda: h.latent_vup(ob, w_uv, y, n_in, rq + rk + dr, H, dv, rk), 3, 8, flush), bytes_=w_uv.numel() * 2.0)
+    qb = q[:B].contiguous()
+    rec(f"latent_absorb decode B={B}", _time(lambda: h.latent_absorb(qb, w_uk, freq, md2.positions, H, dn, dr, dr, rk, mag), 3, 8, flush), bytes_=w_uk.numel() * 2.0)
+    # mixture of experts
+    x = torch.randn(T, W, device=dev).to(bf)
+    wr = (torch.randn(n_routed, W, device=dev) / math.sqrt(W) * 4).to(bf)
+    corr = torch.zeros(n_routed, device=dev).to(bf)
+    rec("moe_route prompt", _time(lambda: h.moe_route(x, wr, corr, s["groups"], s["keep"], top), 3, 8, flush), bytes_=T * W * 2.0)
+    dense, idx, wsel = h.moe_route(x, wr, corr, s["groups"], s["keep"], top)
+    w13 = (torch.randn(E * 2 * ff, W, device=dev) * 0.02).to(bf)
+    w2 = (torch.randn(W, E * ff, device=dev) * 0.02).to(bf)
+
+    def dense_form():
+        act = h.linear_swiglu(x, w13, rowscale=dense, group=ff)
+        return h.linear(act, w2, epi=h.EPI_F32)
+
+    rec("experts prompt (all experts, masked)", _time(dense_form, 2, 5, flush), flops=6.0 * T * top * ff * W,
+        note=f"useful FLOPs (top {top} of {E}); the kernels compute all {E} experts")
+    for M in (1, B):
+        xs, ii, ww = x[:M].contiguous(), idx[:M].contiguous(), wsel[:M].contiguous()
+        live = int((ii < E).sum())
+        rec(f"experts decode (chosen only) M={M}", _time(lambda: h.moe_sparse(xs, w13, w2, ii, ww, E, ff), 3, 8, flush), bytes_=live * 3.0 * ff * W * 2)
+    return rows
+
+
+def run_taruvik(a, peaks: dict) -> dict:
+    dev = torch.device("cuda", torch.cuda.current_device())
+    T, ctx = a.prefill, a.prefill
+    res = {"design": "Taruvik", "dtype": "bf16", "data": "synthetic", "prompt_tokens": T, "peaks": {k: peaks.get(k) for k in ("hbm_gbs", "bf16_tflops")}, "sizes": {}}
+    for name, s in TARUVIK_SIZES.items():
+        t0 = time.time()
+        m = build_taruvik(s, dev)
+        new = end_to_end(m, s["vocab"], T, ctx, (1, 8), a.warmup, a.steps, dev)
+        del m
+        torch.cuda.empty_cache()
+        try:
+            d = build_moe_transformer(s, dev)
+            old = end_to_end(d, s["vocab"], T, ctx, (1, 8), a.warmup, a.steps, dev)
+            del d
+        except Exception as e:  # the neighbour's kernels may not take this size
+            old = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+        torch.cuda.empty_cache()
+        res["sizes"][name] = {"config": s, "layered": new, "moe_transformer": old, "kernels": taruvik_kernel_table(s, T, ctx, peaks, dev),
+                              "seconds": round(time.time() - t0, 1)}
+    return res
+
+
 def run(a, peaks: dict) -> dict:
+    if a.design == "taruvik":
+        return run_taruvik(a, peaks)
     dev = torch.device("cuda", torch.cuda.current_device())
     T, ctx = a.prefill, a.prefill
     res = {"design": "Fesenex", "dtype": "bf16", "data": "synthetic", "prompt_tokens": T, "peaks": {k: peaks.get(k) for k in ("hbm_gbs", "bf16_tflops")}, "sizes": {}}
