@@ -266,15 +266,26 @@ def taruvik_kernel_table(s: dict, T: int, ctx: int, peaks: dict, dev) -> dict:
     Tp = min(T, 1024)  # the exact kernel on a prompt: a shorter one keeps the run short
     mdp = cache.get_input_metadata([Tp])[0]
     qp = qa[:Tp].contiguous()
-    rec(f"attn_latent prompt T={Tp}", _time(lambda: h.attn_latent(qp, cache.cache_k[0], mdp.positions, mdp.q_start, mdp.slots, 1, ctx + 8, H, rk, dr, 0.07,
+    rec(f"attn_latent (latent form, portions of prompts and fp32) T={Tp}", _time(lambda: h.attn_latent(qp, cache.cache_k[0], mdp.positions, mdp.q_start, mdp.slots, 1, ctx + 8, H, rk, dr, 0.07,
                                                                  splits=h.attn_splits(Tp, H, ctx + 8)), 1, 3, flush),
         flops=2.0 * H * (2 * rk + dr) * Tp * (Tp + 1) / 2, note="exact fp32 FMA kernel, no tensor cores")
     cache.reset(); cache.init_kvseqlens(B); cache.update_seqlens([ctx] * B)
     md2 = cache.get_input_metadata([1] * B)[0]
     q2 = qa[:B].contiguous()
-    rec(f"attn_latent decode B={B} ctx={ctx}", _time(lambda: h.attn_latent(q2, cache.cache_k[0], md2.positions, md2.q_start, md2.slots, B, ctx + 8, H, rk, dr, 0.07,
+    rec(f"attn_latent (a CTA per head) decode B={B} ctx={ctx}", _time(lambda: h.attn_latent(q2, cache.cache_k[0], md2.positions, md2.q_start, md2.slots, B, ctx + 8, H, rk, dr, 0.07,
                                                                             splits=h.attn_splits(B, H, ctx + 8)), 3, 8, flush),
         bytes_=B * (ctx + 1) * (rk + dr) * 2.0, note="bytes: every latent row once; each head's CTAs re-read them through L2")
+    rec(f"attn_latent_decode (rows shared by the heads) B={B} ctx={ctx}",
+        _time(lambda: h.attn_latent_decode(q2, cache.cache_k[0], md2.positions, md2.slots, B, ctx + 8, H, rk, dr, 0.07), 3, 8, flush),
+        bytes_=B * (ctx + 1) * (rk + dr) * 2.0)
+    if (dn + dr, dv) in h.FLASH_SIZES:  # whole prompts: multi-head attention over written-out keys and values
+        kf = torch.randn(T, H, dn + dr, device=dev).to(bf)
+        vf = torch.randn(T, H, dv, device=dev).to(bf)
+        qr = torch.randn(T, H * (dn + dr), device=dev).to(bf)
+        of = torch.empty(T, H * dv, device=dev, dtype=bf)
+        rec(f"prompt attention over written-out keys (attn_bias_flash, {dn + dr}/{dv}) T={T}",
+            _time(lambda: h.attn_bias(qr, kf, vf, None, md.positions, md.q_start, h.iota(1, dev), of, 1, T, H, H, dn + dr, dv, 0.07, n_tiles=(T + 63) // 64), 2, 5, flush),
+            flops=2.0 * H * (dn + dr + dv) * T * (T + 1) / 2)
     o_lat = torch.randn(T, H * rk, device=dev).to(bf)
     w_uv = (torch.randn(H * dv, rk, device=dev) / math.sqrt(rk)).to(bf)
     rec("latent_vup prompt", _time(lambda: h.latent_vup(o_lat, w_uv, y, n_in, rq + rk + dr, H, dv, rk), 2, 5, flush), flops=2.0 * T * H * dv * rk)

@@ -48,7 +48,7 @@ int mbh_attn_prep(const void* qkv, const void* qnorm, const void* knorm, const v
 
 /* Causal softmax attention of q[T, H*d] over the ring: token t of sequence b (q_start[B+1]) at position positions[t] sees keys
  * 0..position of cache block slots[b] (W rows each, key j in row j % W); score = q.k * scale + bias_tab[min(distance, n_tab-1), h]
- * (fp32 [n_tab, H]).  out [T, H*e].
+ * (fp32 [n_tab, H]; null: no bias).  out [T, H*e].
  * n_tiles > 0 (prompts): the number of 64-query tiles, sum over sequences of ceil(len / 64); with bf16 storage and key/value
  * sizes among {32, 64, 128} the tensor-core kernel runs (P rounded to bf16 before P V).  n_tiles = 0: the exact fp32 kernel,
  * with `splits` > 1 CTAs per (token, head) along the keys (decode) and their partial results in scratch (fp32 [T*H, splits, 2 + e]). */
@@ -87,15 +87,31 @@ int mbh_latent_prep(const void* y, const void* qnorm, const void* cnorm, const v
                     void* ring, int64_t T, int64_t pitch, int64_t q_rank, int64_t kv_rank, int64_t rot_dim, int64_t rot_dims, float eps, float mag,
                     int dt, void* stream);
 
-/* q [T, H, dn + rot_dim] -> qa [T, H, kv_rank + rot_dim] = [W_uk[h]^T q[:dn] | rot(q[dn:])], w_uk [H * dn, kv_rank]. */
+/* q [T, H, dn + rot_dim] -> qa [T, H, kv_rank + rot_dim] = [W_uk[h]^T q[:dn] | rot(q[dn:])], w_uk [H * dn, kv_rank].
+ * w_uk null: no folding, qa [T, H, dn + rot_dim] = [q[:dn] | rot(q[dn:])]. */
 int mbh_latent_absorb(const void* q, const void* w_uk, const void* freq, const void* positions, void* qa, int64_t T, int64_t H, int64_t dn,
                       int64_t rot_dim, int64_t rot_dims, int64_t kv_rank, float mag, int dt, void* stream);
+
+/* Keys and values per head of whole prompts, for ordinary multi-head attention (mbh_attn_bias with bias_tab null): token t at
+ * position p of sequence b goes to row b * Wt + p of kfull [B * Wt, H, dn + rot_dim] = [kn[t, h] | rotated key part of ring row
+ * cache_rows[t]] and vfull [B * Wt, H, dv] = v[t, h].  kn [T, H * dn], v [T, H * dv]. */
+int mbh_latent_expand(const void* kn, const void* v, const void* ring, const void* positions, const void* cache_rows, const void* q_start, void* kfull,
+                      void* vfull, int64_t T, int64_t B, int64_t Wt, int64_t H, int64_t dn, int64_t rot_dim, int64_t dv, int64_t kv_rank, int dt,
+                      void* stream);
+
+/* out [T, H, dv] *= sigmoid(gate[t * g_pitch + g_off + h]), in place. */
+int mbh_head_gate(void* out, const void* gate, int64_t g_pitch, int64_t g_off, int64_t T, int64_t H, int64_t dv, int dt, void* stream);
 
 /* Causal softmax attention of qa over latent rows: score = qa . ring row * scale, value = the row's first kv_rank entries;
  * o_lat [T, H, kv_rank].  Ring addressing, splits and scratch as mbh_attn_bias (exact fp32 kernel, one key/value head). */
 int mbh_attn_latent(const void* qa, const void* ring, const void* positions, const void* q_start, const void* slots, void* o_lat, int64_t T,
                     int64_t B, int64_t W, int64_t H, int64_t kv_rank, int64_t rot_dim, float scale, int64_t splits, void* scratch, int dt,
                     void* stream);
+
+/* The same for one token per sequence (token b belongs to sequence b; qa [B, H, kv_rank + rot_dim]): each CTA reads a span of one
+ * sequence's rows once for all heads.  H <= 32, kv_rank <= 512; scratch fp32 [B * H, splits, 2 + kv_rank], splits >= 1. */
+int mbh_attn_latent_decode(const void* qa, const void* ring, const void* positions, const void* slots, void* o_lat, int64_t B, int64_t W, int64_t H,
+                           int64_t kv_rank, int64_t rot_dim, float scale, int64_t splits, void* scratch, int dt, void* stream);
 
 /* out [T, H * dv] = (W_uv[h] o_lat[t, h]) * sigmoid(gate[t * g_pitch + g_off + h]); w_uv [H * dv, kv_rank]; gate null: no gate. */
 int mbh_latent_vup(const void* o_lat, const void* w_uv, const void* gate, int64_t g_pitch, int64_t g_off, void* out, int64_t T, int64_t H,

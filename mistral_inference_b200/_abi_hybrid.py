@@ -36,7 +36,10 @@ _SIGNATURES = {
     "mbh_swiglu_epilogue": (c_int, [P, P, I, I, P, I, I, c_int, P]),
     "mbh_latent_prep": (c_int, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, c_int, P]),
     "mbh_latent_absorb": (c_int, [P, P, P, P, P, I, I, I, I, I, I, F, c_int, P]),
+    "mbh_latent_expand": (c_int, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, c_int, P]),
+    "mbh_head_gate": (c_int, [P, P, I, I, I, I, I, c_int, P]),
     "mbh_attn_latent": (c_int, [P, P, P, P, P, P, I, I, I, I, I, I, F, I, P, c_int, P]),
+    "mbh_attn_latent_decode": (c_int, [P, P, P, P, P, I, I, I, I, I, F, I, P, c_int, P]),
     "mbh_latent_vup": (c_int, [P, P, P, I, I, P, I, I, I, I, c_int, P]),
     "mbh_moe_route": (c_int, [P, P, P, P, P, P, I, I, I, I, I, I, c_int, P]),
     "mbh_moe_sparse": (c_int, [P, P, P, P, P, P, P, I, I, I, I, I, c_int, P]),
@@ -151,9 +154,9 @@ def attn_prep(qkv, qnorm, knorm, positions, cache_rows, q_out, cache_k, cache_v,
 def attn_bias(q, cache_k, cache_v, bias_tab, positions, q_start, slots, out, B: int, W: int, H: int, G: int, d: int, e: int, scale: float,
               n_tiles: int = 0, splits: int = 1) -> None:
     """n_tiles = sum over sequences of ceil(len / 64) selects the tensor-core prompt kernel (bf16); 0 the exact fp32 one."""
-    assert bias_tab.dtype == torch.float32 and bias_tab.shape[1] == H
+    assert bias_tab is None or (bias_tab.dtype == torch.float32 and bias_tab.shape[1] == H)
     scratch = torch.empty(q.shape[0] * H * splits * (2 + e), dtype=torch.float32, device=q.device) if splits > 1 and n_tiles == 0 else None
-    _check(lib().mbh_attn_bias(_ptr(q), _ptr(cache_k), _ptr(cache_v), _ptr(bias_tab), bias_tab.shape[0], _ptr(positions), _ptr(q_start), _ptr(slots),
+    _check(lib().mbh_attn_bias(_ptr(q), _ptr(cache_k), _ptr(cache_v), _ptr(bias_tab), bias_tab.shape[0] if bias_tab is not None else 0, _ptr(positions), _ptr(q_start), _ptr(slots),
                                _ptr(out), q.shape[0], B, W, H, G, d, e, scale, n_tiles, splits, _ptr(scratch), dt_of(q.dtype), _stream()), "mbh_attn_bias")
 
 
@@ -258,9 +261,33 @@ def latent_prep(y, qnorm, cnorm, freq, positions, cache_rows, ring, q_rank: int,
     return cq
 
 
+FLASH_SIZES = {(32, 32), (64, 32), (64, 64), (128, 64), (64, 128), (128, 128), (96, 64), (192, 128)}  # (key, value) sizes of the tensor-core prompt kernel
+_iota: dict = {}
+
+
+def iota(n: int, device: torch.device) -> torch.Tensor:
+    """int32 [n] = 0 .. n-1 (row blocks of a temporary ring), made once per device and length."""
+    if (device, n) not in _iota:
+        _iota[(device, n)] = torch.arange(n, dtype=torch.int32, device=device)
+    return _iota[(device, n)]
+
+
+def latent_expand(kn, v, ring, positions, cache_rows, q_start, B: int, Wt: int, H: int, dn: int, rot_dim: int, dv: int, kv_rank: int):
+    kfull = torch.empty(B * Wt, H, dn + rot_dim, dtype=kn.dtype, device=kn.device)
+    vfull = torch.empty(B * Wt, H, dv, dtype=kn.dtype, device=kn.device)
+    _check(lib().mbh_latent_expand(_ptr(kn), _ptr(v), _ptr(ring), _ptr(positions), _ptr(cache_rows), _ptr(q_start), _ptr(kfull), _ptr(vfull), kn.shape[0],
+                                   B, Wt, H, dn, rot_dim, dv, kv_rank, dt_of(kn.dtype), _stream()), "mbh_latent_expand")
+    return kfull, vfull
+
+
+def head_gate(out, gate, g_pitch: int, g_off: int, H: int, dv: int) -> None:
+    _check(lib().mbh_head_gate(_ptr(out), _ptr(gate), g_pitch, g_off, out.shape[0], H, dv, dt_of(out.dtype), _stream()), "mbh_head_gate")
+
+
 def latent_absorb(q, w_uk, freq, positions, H: int, dn: int, rot_dim: int, rot_dims: int, kv_rank: int, mag: float) -> torch.Tensor:
+    """w_uk None: the queries are only rotated ([T, H * (dn + rot_dim)])."""
     T = q.shape[0]
-    qa = torch.empty(T, H * (kv_rank + rot_dim), dtype=q.dtype, device=q.device)
+    qa = torch.empty(T, H * ((kv_rank if w_uk is not None else dn) + rot_dim), dtype=q.dtype, device=q.device)
     _check(lib().mbh_latent_absorb(_ptr(q), _ptr(w_uk), _ptr(freq), _ptr(positions), _ptr(qa), T, H, dn, rot_dim, rot_dims, kv_rank, mag,
                                    dt_of(q.dtype), _stream()), "mbh_latent_absorb")
     return qa
@@ -272,6 +299,24 @@ def attn_latent(qa, ring, positions, q_start, slots, B: int, W: int, H: int, kv_
     scratch = torch.empty(T * H * splits * (2 + kv_rank), dtype=torch.float32, device=qa.device) if splits > 1 else None
     _check(lib().mbh_attn_latent(_ptr(qa), _ptr(ring), _ptr(positions), _ptr(q_start), _ptr(slots), _ptr(o), T, B, W, H, kv_rank, rot_dim, scale,
                                  splits, _ptr(scratch), dt_of(qa.dtype), _stream()), "mbh_attn_latent")
+    return o
+
+
+LATENT_DECODE_MAX_HEADS, LATENT_DECODE_MAX_RANK = 32, 512
+
+
+def latent_decode_splits(B: int, W: int, n_sm: int = 148) -> int:
+    """CTAs per sequence along the keys: two CTAs per SM over the batch, at least 64 ring rows each (batch and ring size only, so a
+    captured decode graph stays valid as the context grows)."""
+    return int(max(1, min((2 * n_sm) // B, (W + 63) // 64, 64)))
+
+
+def attn_latent_decode(qa, ring, positions, slots, B: int, W: int, H: int, kv_rank: int, rot_dim: int, scale: float) -> torch.Tensor:
+    splits = latent_decode_splits(B, W)
+    o = torch.empty(B, H * kv_rank, dtype=qa.dtype, device=qa.device)
+    scratch = torch.empty(B * H * splits * (2 + kv_rank), dtype=torch.float32, device=qa.device)
+    _check(lib().mbh_attn_latent_decode(_ptr(qa), _ptr(ring), _ptr(positions), _ptr(slots), _ptr(o), B, W, H, kv_rank, rot_dim, scale, splits,
+                                        _ptr(scratch), dt_of(qa.dtype), _stream()), "mbh_attn_latent_decode")
     return o
 
 

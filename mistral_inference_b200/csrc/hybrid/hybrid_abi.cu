@@ -54,7 +54,7 @@ template <typename T> static void run_layernorm(const void* x32, const void* w, 
 }
 template <typename T> static void run_attn_wide(const AttnArgs& a, size_t smem, cudaStream_t st) {
     attn_bias_kernel<T, AT_MAXR_WIDE><<<dim3((unsigned)(a.T * a.H), (unsigned)a.splits), AT_WARPS * 32, smem, st>>>(a);
-    if (a.splits > 1) attn_merge_kernel<T><<<(unsigned)(a.T * a.H), 64, 0, st>>>(a.scratch, (T*)a.out, a.splits, a.e);
+    if (a.splits > 1) attn_merge_kernel<T><<<(unsigned)(a.T * a.H), 128, 0, st>>>(a.scratch, (T*)a.out, a.splits, a.e);
 }
 template <typename T> static void run_moe_sparse(const MoeSparseArgs& a, int64_t T_, cudaStream_t st) {
     moe_gateup_sparse_kernel<T><<<dim3((unsigned)((a.ff + MOE_WARPS - 1) / MOE_WARPS), (unsigned)(T_ * a.top)), MOE_WARPS * 32, 0, st>>>(a);
@@ -70,11 +70,27 @@ template <typename T> static void run_epilogue(const LinearArgs& a, const void* 
 template <typename T> static void run_prep(const AttnPrepArgs& a, int64_t T_, cudaStream_t st) { attn_prep_kernel<T><<<(unsigned)T_, 128, 0, st>>>(a); }
 template <typename T> static void run_attn(const AttnArgs& a, size_t smem, cudaStream_t st) {
     attn_bias_kernel<T><<<dim3((unsigned)(a.T * a.H), (unsigned)a.splits), AT_WARPS * 32, smem, st>>>(a);
-    if (a.splits > 1) attn_merge_kernel<T><<<(unsigned)(a.T * a.H), 64, 0, st>>>(a.scratch, (T*)a.out, a.splits, a.e);
+    if (a.splits > 1) attn_merge_kernel<T><<<(unsigned)(a.T * a.H), 128, 0, st>>>(a.scratch, (T*)a.out, a.splits, a.e);
 }
 template <typename T> static void run_headnorm(const void* o32, const void* w, const void* g, int64_t g_pitch, int64_t g_off, void* y, int64_t T_,
                                                int64_t N, float eps, cudaStream_t st) {
     gated_headnorm_kernel<T><<<(unsigned)T_, 128, 0, st>>>((const float*)o32, (const T*)w, (const T*)g, (int)g_pitch, (int)g_off, (T*)y, (int)N, eps);
+}
+
+template <typename T, int HPW> static cudaError_t run_latent_decode(const LatentDecodeArgs& a, void* out, size_t smem, cudaStream_t st) {
+    cudaError_t e = cudaFuncSetAttribute(attn_latent_decode_kernel<T, HPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e) return e;
+    attn_latent_decode_kernel<T, HPW><<<dim3((unsigned)a.B, (unsigned)a.splits), LD_WARPS * 32, smem, st>>>(a);
+    attn_merge_kernel<T><<<(unsigned)(a.B * a.H), 128, 0, st>>>(a.scratch, (T*)out, a.splits, a.kv_rank);
+    return cudaGetLastError();
+}
+template <typename T> static cudaError_t launch_latent_decode(const LatentDecodeArgs& a, void* out, cudaStream_t st) {
+    const int d = a.kv_rank + a.rot_dim, kp = d + (sizeof(T) == 2 ? 2 : 1);
+    const size_t smem = sizeof(float) * ((size_t)a.H * d + (size_t)a.H * LD_KT) + sizeof(T) * (size_t)LD_KT * kp;
+    if (smem > 220 * 1024) return cudaErrorInvalidValue;
+    if (a.H <= LD_WARPS) return run_latent_decode<T, 1>(a, out, smem, st);
+    if (a.H <= 2 * LD_WARPS) return run_latent_decode<T, 2>(a, out, smem, st);
+    return run_latent_decode<T, 4>(a, out, smem, st);
 }
 
 extern "C" {
@@ -137,6 +153,7 @@ int mbh_attn_bias(const void* q, const void* cache_k, const void* cache_v, const
     if (T == 0) return 0;
     if (e > 32 * AT_MAXR) return bad("mbh_attn_bias: value size above 256");
     if (H % G) return bad("mbh_attn_bias: heads must be a multiple of kv heads");
+    if (splits > AT_MAX_SPLITS) return bad("mbh_attn_bias: at most 64 splits");
     AttnArgs a{q, cache_k, cache_v, (const float*)bias_tab, (int)n_tab, (const int*)positions, (const int*)q_start, (const int*)slots, out,
                (int)T, (int)B, (int)W, (int)H, (int)G, (int)d, (int)e, scale, (int)(splits > 1 && scratch ? splits : 1), (float*)scratch};
     const size_t smem = sizeof(float) * ((size_t)d + AT_WARPS * AT_CHUNK + AT_WARPS * (2 + 32 * AT_MAXR));
@@ -229,9 +246,29 @@ int mbh_latent_absorb(const void* q, const void* w_uk, const void* freq, const v
     if (rot_dims > rot_dim || (rot_dims & 1)) return bad("mbh_latent_absorb: rot_dims must be even and at most rot_dim");
     LatentAbsorbArgs a{q, w_uk, (const double*)freq, (const int*)positions, qa, (int)H, (int)dn, (int)rot_dim, (int)rot_dims, (int)kv_rank, mag};
     cudaStream_t st = (cudaStream_t)stream;
-    DISPATCH(dt, latent_absorb_kernel<ST><<<(unsigned)(T * H), 128, sizeof(float) * (size_t)dn, st>>>(a));
+    DISPATCH(dt, latent_absorb_kernel<ST><<<dim3((unsigned)(T * H), (unsigned)(w_uk ? (kv_rank + 127) / 128 : 1)), 128, sizeof(float) * (size_t)dn, st>>>(a));
     cudaError_t e = cudaGetLastError();
     return e ? fail(e, "mbh_latent_absorb") : 0;
+}
+
+int mbh_latent_expand(const void* kn, const void* v, const void* ring, const void* positions, const void* cache_rows, const void* q_start, void* kfull,
+                      void* vfull, int64_t T, int64_t B, int64_t Wt, int64_t H, int64_t dn, int64_t rot_dim, int64_t dv, int64_t kv_rank, int dt,
+                      void* stream) {
+    if (T == 0) return 0;
+    LatentExpandArgs a{kn, v, ring, (const int*)positions, (const int*)cache_rows, (const int*)q_start, kfull, vfull,
+                       (int)B, (int)Wt, (int)H, (int)dn, (int)rot_dim, (int)dv, (int)kv_rank};
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, latent_expand_kernel<ST><<<(unsigned)T, 128, 0, st>>>(a));
+    cudaError_t e = cudaGetLastError();
+    return e ? fail(e, "mbh_latent_expand") : 0;
+}
+
+int mbh_head_gate(void* out, const void* gate, int64_t g_pitch, int64_t g_off, int64_t T, int64_t H, int64_t dv, int dt, void* stream) {
+    if (T == 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    DISPATCH(dt, head_gate_kernel<ST><<<(unsigned)T, 256, 0, st>>>((ST*)out, (const ST*)gate, (int)g_pitch, (int)g_off, (int)H, (int)dv));
+    cudaError_t e = cudaGetLastError();
+    return e ? fail(e, "mbh_head_gate") : 0;
 }
 
 int mbh_attn_latent(const void* qa, const void* ring, const void* positions, const void* q_start, const void* slots, void* o_lat, int64_t T,
@@ -239,6 +276,7 @@ int mbh_attn_latent(const void* qa, const void* ring, const void* positions, con
                     void* stream) {
     if (T == 0) return 0;
     if (kv_rank > 32 * AT_MAXR_WIDE) return bad("mbh_attn_latent: latent size above 512");
+    if (splits > AT_MAX_SPLITS) return bad("mbh_attn_latent: at most 64 splits");
     const int d = (int)(kv_rank + rot_dim);
     AttnArgs a{qa, ring, ring, nullptr, 0, (const int*)positions, (const int*)q_start, (const int*)slots, o_lat,
                (int)T, (int)B, (int)W, (int)H, 1, d, (int)kv_rank, scale, (int)(splits > 1 && scratch ? splits : 1), (float*)scratch, d, d};
@@ -251,12 +289,26 @@ int mbh_attn_latent(const void* qa, const void* ring, const void* positions, con
     return e ? fail(e, "mbh_attn_latent") : 0;
 }
 
+int mbh_attn_latent_decode(const void* qa, const void* ring, const void* positions, const void* slots, void* o_lat, int64_t B, int64_t W, int64_t H,
+                           int64_t kv_rank, int64_t rot_dim, float scale, int64_t splits, void* scratch, int dt, void* stream) {
+    if (B == 0) return 0;
+    if (H > 4 * LD_WARPS || kv_rank > 32 * LD_CPL) return bad("mbh_attn_latent_decode: at most 32 heads and a latent of 512");
+    if (splits < 1 || splits > AT_MAX_SPLITS || !scratch) return bad("mbh_attn_latent_decode: needs 1 <= splits <= 64 and scratch");
+    LatentDecodeArgs a{qa, ring, (const int*)positions, (const int*)slots, (float*)scratch, (int)B, (int)W, (int)H, (int)kv_rank, (int)rot_dim, scale,
+                       (int)splits};
+    cudaError_t e = cudaSuccess;
+    DISPATCH(dt, e = launch_latent_decode<ST>(a, o_lat, (cudaStream_t)stream));
+    return e ? fail(e, "mbh_attn_latent_decode") : 0;
+}
+
 int mbh_latent_vup(const void* o_lat, const void* w_uv, const void* gate, int64_t g_pitch, int64_t g_off, void* out, int64_t T, int64_t H,
                    int64_t dv, int64_t kv_rank, int dt, void* stream) {
     if (T == 0) return 0;
     LatentVupArgs a{o_lat, w_uv, gate, out, (int)H, (int)dv, (int)kv_rank, (int)g_pitch, (int)g_off};
     cudaStream_t st = (cudaStream_t)stream;
-    DISPATCH(dt, latent_vup_kernel<ST><<<(unsigned)(T * H), 128, sizeof(float) * (size_t)kv_rank, st>>>(a));
+    // few tokens: a CTA per four value columns, so that a decode step fills the GPU; prompts: one CTA per (token, head)
+    const unsigned vblocks = (T * H < 2048) ? (unsigned)((dv + 3) / 4) : 1u;
+    DISPATCH(dt, latent_vup_kernel<ST><<<dim3((unsigned)(T * H), vblocks), 128, sizeof(float) * (size_t)kv_rank, st>>>(a));
     cudaError_t e = cudaGetLastError();
     return e ? fail(e, "mbh_latent_vup") : 0;
 }
@@ -270,7 +322,7 @@ int mbh_moe_route(const void* h, const void* w_router, const void* correction, v
     if (smem > 48 * 1024) return bad("mbh_moe_route: too many routed outputs");
     MoeRouteArgs a{h, w_router, correction, (float*)dense, (int*)idx, (float*)wsel, (int)width, (int)n, (int)groups, (int)keep, (int)top};
     cudaStream_t st = (cudaStream_t)stream;
-    DISPATCH(dt, moe_route_kernel<ST><<<(unsigned)T, 128, smem, st>>>(a));
+    DISPATCH(dt, moe_route_kernel<ST><<<(unsigned)T, MOE_ROUTE_THREADS, smem, st>>>(a));
     cudaError_t e = cudaGetLastError();
     return e ? fail(e, "mbh_moe_route") : 0;
 }

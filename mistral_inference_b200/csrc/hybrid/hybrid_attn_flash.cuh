@@ -66,7 +66,7 @@ __global__ void __launch_bounds__(128) attn_bias_flash_kernel(AttnArgs a) {
     const size_t kstride = (size_t)a.G * D, vstride = (size_t)a.G * E;
     const bf16* K = static_cast<const bf16*>(a.cache_k) + base * kstride + (size_t)g * D;
     const bf16* V = static_cast<const bf16*>(a.cache_v) + base * vstride + (size_t)g * E;
-    const float* bias = a.bias_tab + h;
+    const float* bias = a.bias_tab ? a.bias_tab + h : nullptr;  // null: no bias
     const int last_tab = a.n_tab - 1;
 
     for (int j0 = 0; j0 <= pos_last; j0 += FA_BK) {
@@ -104,8 +104,8 @@ __global__ void __launch_bounds__(128) attn_bias_flash_kernel(AttnArgs a) {
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 const int j = j0 + nt * 8 + tig * 2 + c;
-                const float x0 = (j <= p0) ? s[nt][c] * a.scale + bias[(size_t)min(p0 - j, last_tab) * a.H] : -INFINITY;
-                const float x1 = (j <= p1) ? s[nt][2 + c] * a.scale + bias[(size_t)min(p1 - j, last_tab) * a.H] : -INFINITY;
+                const float x0 = (j <= p0) ? s[nt][c] * a.scale + (bias ? bias[(size_t)min(p0 - j, last_tab) * a.H] : 0.f) : -INFINITY;
+                const float x1 = (j <= p1) ? s[nt][2 + c] * a.scale + (bias ? bias[(size_t)min(p1 - j, last_tab) * a.H] : 0.f) : -INFINITY;
                 s[nt][c] = x0; s[nt][2 + c] = x1;
                 mx0 = fmaxf(mx0, x0); mx1 = fmaxf(mx1, x1);
             }
@@ -149,7 +149,7 @@ __global__ void __launch_bounds__(128) attn_bias_flash_kernel(AttnArgs a) {
 inline bool launch_attn_flash(const AttnArgs& a, int n_tiles, cudaStream_t st) {
     dim3 grid(n_tiles, a.H);
 #define MBH_FA(DD, EE) if (a.d == DD && a.e == EE) { attn_bias_flash_kernel<DD, EE><<<grid, 128, 0, st>>>(a); return true; }
-    MBH_FA(32, 32) MBH_FA(64, 32) MBH_FA(64, 64) MBH_FA(128, 64) MBH_FA(64, 128) MBH_FA(128, 128)
+    MBH_FA(32, 32) MBH_FA(64, 32) MBH_FA(64, 64) MBH_FA(128, 64) MBH_FA(64, 128) MBH_FA(128, 128) MBH_FA(96, 64) MBH_FA(192, 128)
 #undef MBH_FA
     return false;
 }

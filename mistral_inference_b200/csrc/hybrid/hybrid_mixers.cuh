@@ -252,23 +252,27 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(AttnArgs a) {
     }
 }
 
-// out[t, h, :] from the `splits` partial results of attn_bias_kernel
+// out[t, h, :] from the `splits` (at most AT_MAX_SPLITS) partial results of attn_bias_kernel: the splits' weights exp(m_s - M) are
+// computed once into shared memory, then every thread sums its value columns over the splits (coalesced over the columns)
+constexpr int AT_MAX_SPLITS = 64;
 template <typename T>
 __global__ void attn_merge_kernel(const float* __restrict__ scratch, T* __restrict__ out, int splits, int e) {
+    __shared__ float f[AT_MAX_SPLITS];
+    __shared__ float red[32];
     const float* part = scratch + (size_t)blockIdx.x * splits * (2 + e);
     float M = -INFINITY;
     for (int s = 0; s < splits; ++s) M = fmaxf(M, part[(size_t)s * (2 + e)]);
-    float L = 0.f;
-    for (int s = 0; s < splits; ++s) {
+    float lpart = 0.f;
+    for (int s = threadIdx.x; s < splits; s += blockDim.x) {
         const float m = part[(size_t)s * (2 + e)];
-        if (m != -INFINITY) L += part[(size_t)s * (2 + e) + 1] * expf(m - M);
+        const float w = (m == -INFINITY) ? 0.f : expf(m - M);
+        f[s] = w;
+        lpart += w * part[(size_t)s * (2 + e) + 1];
     }
+    const float L = block_sum(lpart, red);  // its barriers also publish f[]
     for (int c = threadIdx.x; c < e; c += blockDim.x) {
         float o = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float m = part[(size_t)s * (2 + e)];
-            if (m != -INFINITY) o = fmaf(part[(size_t)s * (2 + e) + 2 + c], expf(m - M), o);
-        }
+        for (int s = 0; s < splits; ++s) o = fmaf(part[(size_t)s * (2 + e) + 2 + c], f[s], o);
         out[(size_t)blockIdx.x * e + c] = from_f<T>(o / L);
     }
 }

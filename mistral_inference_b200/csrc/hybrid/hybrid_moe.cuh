@@ -37,9 +37,30 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
     }
 }
 
+// dot product of two rows of K elements over a warp (16-byte loads when both rows allow it); every lane gets the sum
+template <typename T>
+__device__ __forceinline__ float warp_dot(const T* __restrict__ w, const T* __restrict__ x, int K, int lane) {
+    constexpr int V = Vec<T>::N;
+    float acc = 0.f;
+    if (K % V == 0 && ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x)) % 16 == 0)) {
+        for (int k = lane * V; k < K; k += 32 * V) {
+            float wv[V], xv[V];
+            Vec<T>::load(w + k, wv);
+            Vec<T>::load(x + k, xv);
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc = fmaf(wv[i], xv[i], acc);
+        }
+    } else {
+        for (int k = lane; k < K; k += 32) acc = fmaf(to_f(w[k]), to_f(x[k]), acc);
+    }
+    return warp_sum(acc);
+}
+
+constexpr int MOE_ROUTE_THREADS = 256;
+
 // one CTA per token; shared memory: z[n] | choice[n] | gbest[groups] | kept[groups]
 template <typename T>
-__global__ void __launch_bounds__(128) moe_route_kernel(MoeRouteArgs a) {
+__global__ void __launch_bounds__(MOE_ROUTE_THREADS) moe_route_kernel(MoeRouteArgs a) {
     extern __shared__ float sm[];
     float* z = sm;
     float* ch = sm + a.n;
@@ -49,10 +70,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(MoeRouteArgs a) {
     const T* h = static_cast<const T*>(a.h) + (size_t)t * a.width;
     const T* W = static_cast<const T*>(a.w_router);
     for (int e = warp; e < a.n; e += nw) {
-        const T* wr = W + (size_t)e * a.width;
-        float acc = 0.f;
-        for (int i = lane; i < a.width; i += 32) acc = fmaf(to_f(h[i]), to_f(wr[i]), acc);
-        acc = warp_sum(acc);
+        const float acc = warp_dot<T>(W + (size_t)e * a.width, h, a.width, lane);
         if (lane == 0) z[e] = acc;
     }
     __syncthreads();
@@ -107,25 +125,6 @@ __global__ void __launch_bounds__(128) moe_route_kernel(MoeRouteArgs a) {
         }
         __syncwarp();
     }
-}
-
-// dot product of two rows of K elements over a warp (16-byte loads when both rows allow it); every lane gets the sum
-template <typename T>
-__device__ __forceinline__ float warp_dot(const T* __restrict__ w, const T* __restrict__ x, int K, int lane) {
-    constexpr int V = Vec<T>::N;
-    float acc = 0.f;
-    if (K % V == 0 && ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(x)) % 16 == 0)) {
-        for (int k = lane * V; k < K; k += 32 * V) {
-            float wv[V], xv[V];
-            Vec<T>::load(w + k, wv);
-            Vec<T>::load(x + k, xv);
-#pragma unroll
-            for (int i = 0; i < V; ++i) acc = fmaf(wv[i], xv[i], acc);
-        }
-    } else {
-        for (int k = lane; k < K; k += 32) acc = fmaf(to_f(w[k]), to_f(x[k]), acc);
-    }
-    return warp_sum(acc);
 }
 
 struct MoeSparseArgs {

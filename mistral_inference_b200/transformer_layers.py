@@ -370,6 +370,8 @@ class LatentAttention(nn.Module):
         self.wo = nn.Parameter(torch.empty(width, a.heads * a.vdim), requires_grad=False)
         self._freq: Optional[torch.Tensor] = None
         self._mag = 1.0
+        self.shared_decode = True   # decode steps read each latent row once for all heads (else: the per-head kernel)
+        self.expand_prompts = True  # whole bf16 prompts of suitable head sizes run multi-head attention on the tensor cores
 
     def cache_spec(self) -> LayerCacheSpec:
         # one shared "head" whose key row is the latent row; the values are its first kv_rank entries, so no value ring
@@ -389,9 +391,27 @@ class LatentAttention(nn.Module):
         cq = _h.latent_prep(y, self.q_norm, self.c_norm, freq, md.positions, md.cache_rows, view.cache_k, a.q_rank, a.kv_rank, a.rot_dim,
                             a.rot_dims, self.eps, self._mag)
         q = _h.linear(cq, self.w_uq)
+        if (md.first_prefill and hn.dtype == torch.bfloat16 and md.max_seqlen >= FLASH_MIN_QUERIES and (a.dim + a.rot_dim, a.vdim) in _h.FLASH_SIZES
+                and self.expand_prompts):
+            # whole prompts: ordinary multi-head attention on the tensor cores over keys and values written out per head
+            B = len(md.seqlens)
+            # the latents of this call's tokens, gathered from their ring rows (every token of a whole prompt has one)
+            lat = view.cache_k.view(-1, a.kv_rank + a.rot_dim).index_select(0, md.cache_rows.long())[:, : a.kv_rank].contiguous()
+            kfull, vfull = _h.latent_expand(_h.linear(lat, self.w_uk), _h.linear(lat, self.w_uv), view.cache_k, md.positions, md.cache_rows, md.q_start,
+                                            B, md.max_seqlen, a.heads, a.dim, a.rot_dim, a.vdim, a.kv_rank)
+            qr = _h.latent_absorb(q, None, freq, md.positions, a.heads, a.dim, a.rot_dim, a.rot_dims, a.kv_rank, self._mag)
+            out = torch.empty(T, a.heads * a.vdim, dtype=hn.dtype, device=hn.device)
+            _h.attn_bias(qr, kfull, vfull, None, md.positions, md.q_start, _h.iota(B, hn.device), out, B, md.max_seqlen, a.heads, a.heads,
+                         a.dim + a.rot_dim, a.vdim, a.scale, n_tiles=sum((n + 63) // 64 for n in md.seqlens))
+            _h.head_gate(out, y, self.n_in, a.q_rank + a.kv_rank + a.rot_dim, a.heads, a.vdim)
+            return project_out(out, self.wo, x32, post)
         qa = _h.latent_absorb(q, self.w_uk, freq, md.positions, a.heads, a.dim, a.rot_dim, a.rot_dims, a.kv_rank, self._mag)
-        o_lat = _h.attn_latent(qa, view.cache_k, md.positions, md.q_start, md.slots, len(md.seqlens), md.window, a.heads, a.kv_rank, a.rot_dim,
-                               a.scale, splits=_h.attn_splits(T, a.heads, md.window))
+        if not md.prefill and self.shared_decode and a.heads <= _h.LATENT_DECODE_MAX_HEADS and a.kv_rank <= _h.LATENT_DECODE_MAX_RANK:
+            # one token per sequence: every latent row is read once for all heads
+            o_lat = _h.attn_latent_decode(qa, view.cache_k, md.positions, md.slots, T, md.window, a.heads, a.kv_rank, a.rot_dim, a.scale)
+        else:
+            o_lat = _h.attn_latent(qa, view.cache_k, md.positions, md.q_start, md.slots, len(md.seqlens), md.window, a.heads, a.kv_rank, a.rot_dim,
+                                   a.scale, splits=_h.attn_splits(T, a.heads, md.window))
         out = _h.latent_vup(o_lat, self.w_uv, y, self.n_in, a.q_rank + a.kv_rank + a.rot_dim, a.heads, a.vdim, a.kv_rank)
         project_out(out, self.wo, x32, post)
 

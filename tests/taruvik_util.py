@@ -30,7 +30,8 @@ def make_config(width=40, vocab=50, layers=None, loop=None, eps=1e-4) -> dict:
     return cfg
 
 
-def make_weights(cfg: dict, seed: int = 0, dtype=torch.float32, router_gain: float = 4.0) -> Dict[str, torch.Tensor]:
+def make_weights(cfg: dict, seed: int = 0, dtype=torch.float32, router_gain: float = 4.0, correction: float = 0.15) -> Dict[str, torch.Tensor]:
+    """The default correction is comparable to the scores: it changes choices and can make choice scores negative."""
     g = torch.Generator().manual_seed(seed)
     W = cfg["width"]
 
@@ -54,7 +55,7 @@ def make_weights(cfg: dict, seed: int = 0, dtype=torch.float32, router_gain: flo
             r, ff = L["mlp"]["router"], L["mlp"]["expert"]["ff"]
             n = r["experts"] + r.get("identity", 0)
             w[p + "mlp.router"] = mat(n, W, router_gain)
-            w[p + "mlp.correction"] = vec(n, 0.0, 0.15)  # comparable to the scores: changes choices, can make choice scores negative
+            w[p + "mlp.correction"] = vec(n, 0.0, correction)  # comparable to the scores: changes choices, can make choice scores negative
             for e in range(r["experts"]):
                 w[f"{p}mlp.e{e}.gate"], w[f"{p}mlp.e{e}.up"], w[f"{p}mlp.e{e}.down"] = mat(ff, W, 2.0), mat(ff, W, 2.0), mat(W, ff, 2.0)
     return w
