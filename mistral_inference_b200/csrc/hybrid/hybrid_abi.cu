@@ -54,7 +54,7 @@ template <typename T> static void run_layernorm(const void* x32, const void* w, 
 }
 template <typename T> static void run_attn_wide(const AttnArgs& a, size_t smem, cudaStream_t st) {
     attn_bias_kernel<T, AT_MAXR_WIDE><<<dim3((unsigned)(a.T * a.H), (unsigned)a.splits), AT_WARPS * 32, smem, st>>>(a);
-    if (a.splits > 1) attn_merge_kernel<T><<<(unsigned)(a.T * a.H), 128, 0, st>>>(a.scratch, (T*)a.out, a.splits, a.e);
+    if (a.splits > 1) attn_merge_kernel<T><<<dim3((unsigned)(a.T * a.H), (unsigned)((a.e + 127) / 128)), 128, 0, st>>>(a.scratch, (T*)a.out, a.splits, a.e);
 }
 template <typename T> static void run_moe_sparse(const MoeSparseArgs& a, int64_t T_, cudaStream_t st) {
     moe_gateup_sparse_kernel<T><<<dim3((unsigned)((a.ff + MOE_WARPS - 1) / MOE_WARPS), (unsigned)(T_ * a.top)), MOE_WARPS * 32, 0, st>>>(a);
@@ -70,7 +70,7 @@ template <typename T> static void run_epilogue(const LinearArgs& a, const void* 
 template <typename T> static void run_prep(const AttnPrepArgs& a, int64_t T_, cudaStream_t st) { attn_prep_kernel<T><<<(unsigned)T_, 128, 0, st>>>(a); }
 template <typename T> static void run_attn(const AttnArgs& a, size_t smem, cudaStream_t st) {
     attn_bias_kernel<T><<<dim3((unsigned)(a.T * a.H), (unsigned)a.splits), AT_WARPS * 32, smem, st>>>(a);
-    if (a.splits > 1) attn_merge_kernel<T><<<(unsigned)(a.T * a.H), 128, 0, st>>>(a.scratch, (T*)a.out, a.splits, a.e);
+    if (a.splits > 1) attn_merge_kernel<T><<<dim3((unsigned)(a.T * a.H), (unsigned)((a.e + 127) / 128)), 128, 0, st>>>(a.scratch, (T*)a.out, a.splits, a.e);
 }
 template <typename T> static void run_headnorm(const void* o32, const void* w, const void* g, int64_t g_pitch, int64_t g_off, void* y, int64_t T_,
                                                int64_t N, float eps, cudaStream_t st) {
@@ -81,7 +81,7 @@ template <typename T, int HPW> static cudaError_t run_latent_decode(const Latent
     cudaError_t e = cudaFuncSetAttribute(attn_latent_decode_kernel<T, HPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e) return e;
     attn_latent_decode_kernel<T, HPW><<<dim3((unsigned)a.B, (unsigned)a.splits), LD_WARPS * 32, smem, st>>>(a);
-    attn_merge_kernel<T><<<(unsigned)(a.B * a.H), 128, 0, st>>>(a.scratch, (T*)out, a.splits, a.kv_rank);
+    attn_merge_kernel<T><<<dim3((unsigned)(a.B * a.H), (unsigned)((a.kv_rank + 127) / 128)), 128, 0, st>>>(a.scratch, (T*)out, a.splits, a.kv_rank);
     return cudaGetLastError();
 }
 template <typename T> static cudaError_t launch_latent_decode(const LatentDecodeArgs& a, void* out, cudaStream_t st) {

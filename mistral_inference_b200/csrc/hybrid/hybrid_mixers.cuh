@@ -253,7 +253,8 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_bias_kernel(AttnArgs a) {
 }
 
 // out[t, h, :] from the `splits` (at most AT_MAX_SPLITS) partial results of attn_bias_kernel: the splits' weights exp(m_s - M) are
-// computed once into shared memory, then every thread sums its value columns over the splits (coalesced over the columns)
+// computed once into shared memory, then every thread sums ONE value column over the splits (coalesced over the columns, four
+// loads in flight).  grid (token * head, blocks of blockDim columns)
 constexpr int AT_MAX_SPLITS = 64;
 template <typename T>
 __global__ void attn_merge_kernel(const float* __restrict__ scratch, T* __restrict__ out, int splits, int e) {
@@ -270,11 +271,19 @@ __global__ void attn_merge_kernel(const float* __restrict__ scratch, T* __restri
         lpart += w * part[(size_t)s * (2 + e) + 1];
     }
     const float L = block_sum(lpart, red);  // its barriers also publish f[]
-    for (int c = threadIdx.x; c < e; c += blockDim.x) {
-        float o = 0.f;
-        for (int s = 0; s < splits; ++s) o = fmaf(part[(size_t)s * (2 + e) + 2 + c], f[s], o);
-        out[(size_t)blockIdx.x * e + c] = from_f<T>(o / L);
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= e) return;
+    const float* col = part + 2 + c;
+    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+    int s = 0;
+    for (; s + 4 <= splits; s += 4) {
+        o0 = fmaf(col[(size_t)s * (2 + e)], f[s], o0);
+        o1 = fmaf(col[(size_t)(s + 1) * (2 + e)], f[s + 1], o1);
+        o2 = fmaf(col[(size_t)(s + 2) * (2 + e)], f[s + 2], o2);
+        o3 = fmaf(col[(size_t)(s + 3) * (2 + e)], f[s + 3], o3);
     }
+    for (; s < splits; ++s) o0 = fmaf(col[(size_t)s * (2 + e)], f[s], o0);
+    out[(size_t)blockIdx.x * e + c] = from_f<T>(((o0 + o1) + (o2 + o3)) / L);
 }
 
 // ------------------------------------------------------------------------------------------------ lightning attention
