@@ -156,7 +156,10 @@ def _hidden(m, toks, portions=None, taps=None):
 
 
 @pytest.mark.parametrize("mix", [mixer_cfg(), mixer_cfg(heads=1, dim=7, rot_dim=6, vdim=5, q_rank=9, kv_rank=11, rot={"base": 20.0, "dims": 4}),
-                                 mixer_cfg(heads=6, dim=32, rot_dim=16, vdim=32, q_rank=16, kv_rank=300, scale=1.5, rot={"base": 1e4, "dims": 16})])
+                                 mixer_cfg(heads=6, dim=32, rot_dim=16, vdim=32, q_rank=16, kv_rank=300, scale=1.5, rot={"base": 1e4, "dims": 16}),
+                                 # 12 and 20 heads: the decode kernel gives a warp two and four heads
+                                 mixer_cfg(heads=12, dim=8, rot_dim=8, vdim=8, q_rank=16, kv_rank=24, rot={"base": 100.0, "dims": 8}),
+                                 mixer_cfg(heads=20, dim=6, rot_dim=4, vdim=10, q_rank=12, kv_rank=18, scale=0.8, rot={"base": 100.0, "dims": 4})])
 def test_latent_attention_alone(tmp_path, mix):
     """One layer without a feed-forward: prompt, token by token, and portions, against the oracle's residual stream."""
     from mistral_inference_b200.registry import load_model
@@ -171,7 +174,8 @@ def test_latent_attention_alone(tmp_path, mix):
         _close(_hidden(m, toks, portions), taps[0], torch.float32, str(portions))
 
 
-@pytest.mark.parametrize("sizes", [dict(dim=32, rot_dim=32, vdim=32), dict(dim=64, rot_dim=32, vdim=64), dict(dim=16, rot_dim=16, vdim=32)])
+@pytest.mark.parametrize("sizes", [dict(dim=32, rot_dim=32, vdim=32), dict(dim=64, rot_dim=32, vdim=64), dict(dim=16, rot_dim=16, vdim=32),
+                                   dict(dim=128, rot_dim=64, vdim=128)])
 def test_whole_prompts_on_the_tensor_cores(tmp_path, sizes):
     """bf16 prompts of head sizes that the tensor-core kernel takes run as multi-head attention over written-out keys and values;
     the result must agree with the latent form (same model, switch off) and with the oracle, also in a ragged batch, and decoding
@@ -326,3 +330,19 @@ def test_greedy_generation_through_generate(tmp_path, dtype):
                 assert tok == int(logits.argmax()), (k, tok)
             seq.append(tok)
         assert len(lp) == len(p) - 1 + len(g)
+
+
+def test_generate_command_line(tmp_path, capsys):
+    from mistral_inference_b200.main import main
+
+    cfg = make_config(**SHAPES["single"])
+    w = make_weights(cfg, 4)
+    folder = write_folder(tmp_path / "cli", cfg, w)
+    assert main(["generate", str(folder), "--prompt", "5 17 3", "--prompt", "1 2", "--max-tokens", "4", "--dtype", "float32"]) == 0
+    rows = [[int(t) for t in line.split()] for line in capsys.readouterr().out.strip().splitlines()]
+    assert len(rows) == 2 and all(len(r) == 4 for r in rows)
+    for prompt, got in zip(([5, 17, 3], [1, 2]), rows):
+        seq = list(prompt)
+        for tok in got:
+            assert tok == int(O.forward(cfg, w, seq)[-1].argmax())
+            seq.append(tok)
